@@ -73,16 +73,19 @@ def pool_sizes(groups: Sequence[CacheGroup], page_size: int, elem_bytes: int, ma
                max_portion: int, num_pages: Optional[int] = None, budget_bytes: Optional[float] = None) -> List[int]:
     """Pages of every cache group's pool (0 for groups that are not paged).  Groups that keep all keys
     get ``num_pages``, or what ``budget_bytes`` pays for once the windowed groups are paid, at most what
-    ``max_seqs`` requests of ``max_seq_len`` tokens hold and at least 16.  A group whose layers see a window
+    ``max_seqs`` requests of ``max_seq_len`` tokens hold and at least 16.  A group whose layers see a window (or a block of positions)
     needs, per request, the pages under the window and under one step's portion (``max_portion`` tokens)
     plus one - pages behind the window come back when the step is committed - so it gets that many for
     every request slot, never more than the other groups."""
     P = int(page_size)
     cap = max_seqs * ((max_seq_len + P - 1) // P)
-    page_bytes = {g.index: 2 * g.num_planes * P * g.need.num_kv_heads * g.need.head_dim * elem_bytes
+    page_bytes = {g.index: g.num_planes * P * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * elem_bytes
                   for g in groups if g.kind == "paged"}
-    windowed = {g.index: min(cap, max_seqs * ((g.need.window + max_portion + P - 1) // P + 1))
-                for g in groups if g.kind == "paged" and g.need.window is not None}
+    def span(need):          # the most keys a query of this group sees (None: all)
+        sizes = [n for n in (need.window, need.chunk) if n is not None]
+        return min(sizes) if sizes else None
+    windowed = {g.index: min(cap, max_seqs * ((span(g.need) + max_portion + P - 1) // P + 1))
+                for g in groups if g.kind == "paged" and span(g.need) is not None}
     if num_pages:
         full = int(num_pages)
     else:
@@ -225,17 +228,18 @@ class CacheManager:
 
     def commit(self, req_id, n_new: int) -> None:
         """The step has written ``n_new`` tokens: advance the length and give
-        back the pages of windowed groups that no later query can see."""
+        back the pages of windowed and chunked groups that no later query can see."""
         rc = self.requests[req_id]
         rc.length += n_new
         total = (rc.length + self.page_size - 1) // self.page_size
         for gi in self._paged:
             assert total <= len(rc.pages[gi]), "commit beyond the pages appended"
         for g in self.groups:
-            if g.kind != "paged" or g.need.window is None:
+            if g.kind != "paged" or (g.need.window is None and g.need.chunk is None):
                 continue
-            # the next query sits at position `length` and sees keys > length - window
-            first_visible = rc.length - g.need.window + 1
+            # the next query sits at position `length`: under a window it sees keys > length - window,
+            # under a chunked mask those from the start of its own block
+            first_visible = g.need.first_kept(rc.length)
             pages = rc.pages[g.index]
             for idx in range(len(pages)):
                 if (idx + 1) * self.page_size > first_visible:

@@ -2,7 +2,9 @@
 mixers.
 
 Keys and values: per paged group one K and one V tensor
-``[planes, num_pages + 1, page_size, num_kv_heads, head_dim]`` in the engine's
+``[planes, num_pages + 1, page_size, num_kv_heads, head_dim]`` (V with the
+group's value size when that differs; no V at all for a group whose values
+are read out of the key rows) in the engine's
 dtype (andre-fu/prism allocates ``[max_pages, page_size, nkv, hd]`` per layer,
 engine/kv_cache.py:37-46; pages are not cleared on re-use).  The extra last
 page is scratch: padded rows of a captured decode graph write there.  State:
@@ -24,7 +26,7 @@ from .manager import CacheGroup
 class PagedCacheView:
     """One cache plane for one step."""
     k: torch.Tensor                 # [num_pages + 1, P, nkv, hd]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]       # [num_pages + 1, P, nkv, value size]; None: the group keeps no value plane
     block_table: torch.Tensor       # int32 [S, W] on the device
     num_pages: int                  # page ids < num_pages + 1 are legal (the last is scratch)
     page_size: int
@@ -52,7 +54,8 @@ class CacheStorage:
             if g.kind == "paged":
                 shape = (g.num_planes, num_pages[g.index] + 1, page_size, g.need.num_kv_heads, g.need.head_dim)
                 self.k[g.index] = torch.empty(shape, dtype=dtype, device=device)
-                self.v[g.index] = torch.empty(shape, dtype=dtype, device=device)
+                if g.need.value_dim:
+                    self.v[g.index] = torch.empty(shape[:-1] + (g.need.value_dim,), dtype=dtype, device=device)
             elif g.kind == "state":
                 sd = getattr(torch, g.need.state_dtype)
                 self.state[g.index] = torch.zeros((g.num_planes, max_seqs + 1) + tuple(g.need.state_shape),
@@ -78,7 +81,7 @@ class CacheStorage:
             gi, plane, owns = w
             g = self.groups[gi]
             if g.kind == "paged":
-                out.append(PagedCacheView(self.k[gi][plane], self.v[gi][plane], block_tables[gi],
+                out.append(PagedCacheView(self.k[gi][plane], self.v[gi][plane] if gi in self.v else None, block_tables[gi],
                                           self.num_pages[gi] + 1, self.page_size, owns, g.need.window, gi))
             else:
                 out.append(StateCacheView(self.state[gi][plane], slots_dev, host_slots, owns, gi))

@@ -43,16 +43,29 @@ template <> struct VecLoad<__nv_bfloat16> {
     }
 };
 
-constexpr int ATTN_GENERIC_MAXD = 8;   // output dims per lane: head_dim <= 256
+// Which keys the token at position p sees.  All three are causal (keys <= p):
+//   MASK_CAUSAL  every key from 0;
+//   MASK_WINDOW  the last `size` keys, p - size < key;
+//   MASK_CHUNK   the keys of p's own block of `size` positions, blocks counted from position 0.
+__host__ __device__ __forceinline__ int mask_first_key(int kind, int size, int pos) {
+    if (kind == PRISM_MASK_WINDOW && size > 0) return pos - size + 1 > 0 ? pos - size + 1 : 0;
+    if (kind == PRISM_MASK_CHUNK && size > 0) return pos / size * size;
+    return 0;
+}
 
-template <typename T>
-__global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
-                                    int out_stride, const T* __restrict__ kc,
-                                    const T* __restrict__ vc, const int* __restrict__ block_table,
+// MAXD: output dims per lane, value size <= 32 * MAXD.  Keys of `dk` and values of `dv` entries per head may
+// differ in size and live in planes with strides of their own (elements between tokens' rows and between
+// heads), so that the values may also be a slice of the key rows.  `sink` (per query head, or null): one more
+// term exp(sink_h) in the softmax's denominator, with no value; it is not multiplied by `scale`.
+template <typename T, int MAXD>
+__global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, int q_head_stride, T* __restrict__ out,
+                                    int out_stride, const T* __restrict__ kc, long long k_row_stride, int k_head_stride,
+                                    const T* __restrict__ vc, long long v_row_stride, int v_head_stride,
+                                    const int* __restrict__ block_table,
                                     int bt_width, const int* __restrict__ positions,
                                     const int* __restrict__ tok_seg, int Ttot, int nh, int nkv,
-                                    int hd, int page_size, int num_pages, int window, float scale,
-                                    int* err) {
+                                    int dk, int dv, int page_size, int num_pages, int mask_kind, int mask_size,
+                                    float scale, const void* __restrict__ sink, int sink_bf16, int* err) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -63,17 +76,19 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
     const int kvh = h / (nh / nkv);
     const int pos = positions[t];
     const int* bt = block_table + (size_t)tok_seg[t] * bt_width;
-    const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int lo = mask_first_key(mask_kind, mask_size, pos);
 
-    float* qs = smem + warp * hd;
-    for (int d = lane; d < hd; d += 32) qs[d] = to_float(q[(size_t)t * q_stride + h * hd + d]);
+    float* qs = smem + warp * dk;
+    for (int d = lane; d < dk; d += 32) qs[d] = to_float(q[(size_t)t * q_stride + (size_t)h * q_head_stride + d]);
     __syncwarp();
 
-    float acc[ATTN_GENERIC_MAXD];
+    float acc[MAXD];
 #pragma unroll
-    for (int i = 0; i < ATTN_GENERIC_MAXD; ++i) acc[i] = 0.f;
+    for (int i = 0; i < MAXD; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
-    const bool vec_ok = (hd % VecLoad<T>::N) == 0;
+    constexpr int VN = VecLoad<T>::N;
+    const bool vec_ok = dk % VN == 0 && k_row_stride % VN == 0 && k_head_stride % VN == 0 &&
+                        (reinterpret_cast<uintptr_t>(kc) % (VN * sizeof(T))) == 0;
 
     for (int kb = lo; kb <= pos; kb += 32) {
         const int j = kb + lane;
@@ -90,12 +105,12 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
         }
         float s = -INFINITY;
         if (valid) {
-            const T* kr = kc + ((size_t)rowidx * nkv + kvh) * hd;
+            const T* kr = kc + (size_t)rowidx * k_row_stride + (size_t)kvh * k_head_stride;
             float dot = 0.f;
             if (vec_ok) {
-                for (int d = 0; d < hd; d += VecLoad<T>::N) dot += VecLoad<T>::dot(kr + d, qs + d);
+                for (int d = 0; d < dk; d += VN) dot += VecLoad<T>::dot(kr + d, qs + d);
             } else {
-                for (int d = 0; d < hd; ++d) dot += qs[d] * to_float(kr[d]);
+                for (int d = 0; d < dk; ++d) dot += qs[d] * to_float(kr[d]);
             }
             s = dot * scale;
         }
@@ -105,53 +120,101 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
         const float corr = expf(m - m_new);
         l = l * corr + warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < ATTN_GENERIC_MAXD; ++i) acc[i] *= corr;
+        for (int i = 0; i < MAXD; ++i) acc[i] *= corr;
         const int cnt = min(32, pos - kb + 1);
         for (int jj = 0; jj < cnt; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int rj = __shfl_sync(0xffffffffu, rowidx, jj);
             if (rj < 0) continue;
-            const T* vr = vc + ((size_t)rj * nkv + kvh) * hd;
+            const T* vr = vc + (size_t)rj * v_row_stride + (size_t)kvh * v_head_stride;
 #pragma unroll
-            for (int i = 0; i < ATTN_GENERIC_MAXD; ++i) {
+            for (int i = 0; i < MAXD; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) acc[i] += pj * to_float(vr[d]);
+                if (d < dv) acc[i] += pj * to_float(vr[d]);
             }
         }
         m = m_new;
     }
+    if (sink != nullptr) {
+        const float sk = load_param(sink, sink_bf16, h);
+        const float m_all = fmaxf(m, sk);
+        const float corr = expf(m - m_all);          // 0 when no key was seen
+        l = l * corr + expf(sk - m_all);
+#pragma unroll
+        for (int i = 0; i < MAXD; ++i) acc[i] *= corr;
+    }
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-    for (int i = 0; i < ATTN_GENERIC_MAXD; ++i) {
+    for (int i = 0; i < MAXD; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) out[(size_t)t * out_stride + h * hd + d] = from_float<T>(acc[i] * inv);
+        if (d < dv) out[(size_t)t * out_stride + (size_t)h * dv + d] = from_float<T>(acc[i] * inv);
     }
+}
+
+template <typename T, int MAXD>
+static int launch_generic(const void* q, int q_stride, int q_head_stride, void* out, int out_stride, const void* kc,
+                          long long k_row_stride, int k_head_stride, const void* vc, long long v_row_stride,
+                          int v_head_stride, const int* block_table, int bt_width, const int* positions,
+                          const int* tok_seg, int T_, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
+                          int mask_kind, int mask_size, float scale, const void* sink, int sink_bf16, int* err,
+                          cudaStream_t stream) {
+    const int warps = 4;
+    const long long total = (long long)T_ * nh;
+    const int blocks = (int)((total + warps - 1) / warps);
+    const size_t smem = (size_t)warps * dk * sizeof(float);
+    auto kern = attn_generic_kernel<T, MAXD>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<blocks, warps * 32, smem, stream>>>(
+        (const T*)q, q_stride, q_head_stride, (T*)out, out_stride, (const T*)kc, k_row_stride, k_head_stride,
+        (const T*)vc, v_row_stride, v_head_stride, block_table, bt_width, positions, tok_seg, T_, nh, nkv, dk, dv,
+        page_size, num_pages, mask_kind, mask_size, scale, sink, sink_bf16, err);
+    return (int)cudaPeekAtLastError();
 }
 
 }  // namespace prism
 
-// window <= 0: all keys.  Returns cudaErrorInvalidValue for head_dim > 256.
+// Keys of dk and values of dv entries, each plane with its own strides (in elements: between the rows of
+// consecutive cache slots, and between kv heads); mask_kind PRISM_MASK_*; sink: per-head float32 or bf16
+// (sink_dtype) or null.  Returns cudaErrorInvalidValue for dv > 1024 or dk > 12288 / warps.
+PRISM_EXPORT int prism_attention_masked_generic(const void* q, int q_stride, int q_head_stride, void* out,
+                                                int out_stride, const void* kc, long long k_row_stride,
+                                                int k_head_stride, const void* vc, long long v_row_stride,
+                                                int v_head_stride, int dtype, const int* block_table, int bt_width,
+                                                const int* positions, const int* tok_seg, int T, int nh, int nkv,
+                                                int dk, int dv, int page_size, int num_pages, int mask_kind,
+                                                int mask_size, float scale, const void* sink, int sink_dtype,
+                                                int* err, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dv > 1024 || dv <= 0 || dk <= 0 || dk > 8192 || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
+    const int sb = sink_dtype == PRISM_DTYPE_BF16;
+#define PRISM_GENERIC(TT, MD)                                                                                       \
+    return prism::launch_generic<TT, MD>(q, q_stride, q_head_stride, out, out_stride, kc, k_row_stride,             \
+                                         k_head_stride, vc, v_row_stride, v_head_stride, block_table, bt_width,     \
+                                         positions, tok_seg, T, nh, nkv, dk, dv, page_size, num_pages, mask_kind,   \
+                                         mask_size, scale, sink, sb, err, stream)
+    if (dtype == PRISM_DTYPE_BF16) {
+        if (dv <= 256) PRISM_GENERIC(__nv_bfloat16, 8);
+        if (dv <= 512) PRISM_GENERIC(__nv_bfloat16, 16);
+        PRISM_GENERIC(__nv_bfloat16, 32);
+    }
+    if (dv <= 256) PRISM_GENERIC(float, 8);
+    if (dv <= 512) PRISM_GENERIC(float, 16);
+    PRISM_GENERIC(float, 32);
+#undef PRISM_GENERIC
+}
+
+// Keys and values of one size hd in planes [slots, nkv, hd]; window <= 0: all keys.  Returns
+// cudaErrorInvalidValue for head_dim > 256.
 PRISM_EXPORT int prism_attention_generic(const void* q, int q_stride, void* out, int out_stride,
                                          const void* kc, const void* vc, int dtype,
                                          const int* block_table, int bt_width,
                                          const int* positions, const int* tok_seg, int T, int nh,
                                          int nkv, int hd, int page_size, int num_pages, int window,
                                          float scale, int* err, cudaStream_t stream) {
-    if (T <= 0) return 0;
-    if (hd > 32 * prism::ATTN_GENERIC_MAXD || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
-    const int warps = 4;
-    const long long total = (long long)T * nh;
-    const int blocks = (int)((total + warps - 1) / warps);
-    const size_t smem = (size_t)warps * hd * sizeof(float);
-    if (dtype == PRISM_DTYPE_BF16)
-        prism::attn_generic_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
-            (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
-            (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_width, positions,
-            tok_seg, T, nh, nkv, hd, page_size, num_pages, window, scale, err);
-    else
-        prism::attn_generic_kernel<float><<<blocks, warps * 32, smem, stream>>>(
-            (const float*)q, q_stride, (float*)out, out_stride, (const float*)kc, (const float*)vc,
-            block_table, bt_width, positions, tok_seg, T, nh, nkv, hd, page_size, num_pages,
-            window, scale, err);
-    return (int)cudaPeekAtLastError();
+    if (hd > 256) return (int)cudaErrorInvalidValue;
+    return prism_attention_masked_generic(q, q_stride, hd, out, out_stride, kc, (long long)nkv * hd, hd, vc,
+                                          (long long)nkv * hd, hd, dtype, block_table, bt_width, positions, tok_seg,
+                                          T, nh, nkv, hd, hd, page_size, num_pages,
+                                          window > 0 ? PRISM_MASK_WINDOW : PRISM_MASK_CAUSAL, window, scale, nullptr, 0,
+                                          err, stream);
 }

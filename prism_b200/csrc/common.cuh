@@ -26,6 +26,11 @@
 #define PRISM_ERR_POSITION_RANGE 3
 #define PRISM_ERR_WAIT_TIMEOUT 4
 
+// which keys a position sees (all causal): every key, the last `size`, or its own block of `size` positions
+#define PRISM_MASK_CAUSAL 0
+#define PRISM_MASK_WINDOW 1
+#define PRISM_MASK_CHUNK 2
+
 #define PRISM_EXPORT extern "C" __attribute__((visibility("default")))
 
 namespace prism {

@@ -1,6 +1,6 @@
 // Token embedding: out[t, :] = table[ids[t], :] as float32 (the residual
-// stream is float32 in both precisions).  No scaling of the embeddings
-// (andre-fu/prism engine/executor.py:74-75).
+// stream is float32 in both precisions), times `scale` in float32 (1 for models
+// that do not scale their embeddings: andre-fu/prism engine/executor.py:74-75).
 #include "common.cuh"
 #include "vec.cuh"
 
@@ -8,7 +8,7 @@ namespace prism {
 
 template <typename W>
 __global__ void embed_kernel(const int* __restrict__ ids, const W* __restrict__ table,
-                             float* __restrict__ out, int H, int V, int* err) {
+                             float* __restrict__ out, int H, int V, float scale, int* err) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -24,22 +24,24 @@ __global__ void embed_kernel(const int* __restrict__ ids, const W* __restrict__ 
         for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
             float v[8];
             load8(row + i, v);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] *= scale;
             store8(o + i, v);
         }
         return;
     }
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]) * scale;
 }
 
 }  // namespace prism
 
 PRISM_EXPORT int prism_embed(const int* ids, const void* table, int table_dtype, float* out,
-                             int T, int H, int V, int* err, cudaStream_t stream) {
+                             int T, int H, int V, float scale, int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
     if (table_dtype == PRISM_DTYPE_BF16)
         return (int)prism::launch_kernel(prism::embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, ids,
-                                         (const __nv_bfloat16*)table, out, H, V, err);
+                                         (const __nv_bfloat16*)table, out, H, V, scale, err);
     return (int)prism::launch_kernel(prism::embed_kernel<float>, dim3(T), dim3(threads), 0, stream, ids,
-                                     (const float*)table, out, H, V, err);
+                                     (const float*)table, out, H, V, scale, err);
 }

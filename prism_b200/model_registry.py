@@ -1,5 +1,5 @@
-"""Registry from an architecture's name (``architectures[0]`` of config.json)
-to what builds it: a typed-config parser and a function from that config to a
+"""Registry from an architecture's name (``architectures[0]`` of config.json,
+or its ``architecture`` string) to what builds it: a typed-config parser and a function from that config to a
 ``ModelSpec``.
 
 andre-fu/prism's file of this name is a checkpoint LRU
@@ -64,6 +64,10 @@ def resolve(raw_config: dict) -> Architecture:
     """The architecture a raw config.json names."""
     _load_builtin()
     archs = raw_config.get("architectures") or []
+    if isinstance(archs, str):
+        archs = [archs]
+    if not archs and isinstance(raw_config.get("architecture"), str):
+        archs = [raw_config["architecture"]]          # some exporters name one architecture, as a string
     if not archs:
         raise ConfigError(f"config.json has no 'architectures'; registered: {registered_architectures()}")
     name = archs[0]

@@ -81,7 +81,7 @@ _p, _i, _f, _ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlo
 
 
 class _Sig:
-    prism_embed = [_p, _p, _i, _p, _i, _i, _i, _p, _p]
+    prism_embed = [_p, _p, _i, _p, _i, _i, _i, _f, _p, _p]
     prism_add_rmsnorm = [_p, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _p, _i, _i, _p]
     prism_rope_table = [_p, _p, _i, _i, _p, _p]
     prism_rope_kv_write_partial = [_p, _i, _p, _i, _p, _i, _i, _p, _p, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _i,
@@ -90,6 +90,13 @@ class _Sig:
                            _i, _i, _p, _p]
     prism_attention_generic = [_p, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
                                _i, _f, _p, _p]
+    prism_attention_masked_generic = [_p, _i, _i, _p, _i, _p, _ll, _i, _p, _ll, _i, _i, _p, _i, _p, _p, _i, _i, _i,
+                                      _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _p]
+    prism_cache_store = [_p, _ll, _p, _i, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
+    prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
+    prism_rotate_slice = [_p, _ll, _i, _p, _ll, _i, _i, _i, _i, _p, _p, _i, _i, _p]
+    prism_activation = [_p, _ll, _p, _ll, _i, _i, _i, _i, _p]
+    prism_rms_rows = [_p, _ll, _p, _i, _f, _p, _ll, _i, _i, _i, _p]
     prism_attention_bf16_supported = [_i, _i, _i]
     prism_attention_decode_bf16 = [_p, _i, _p, _i, _p, _p, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _f,
                                    _p, _p, _i, _p, _p, _i, _p, _p]
@@ -140,15 +147,15 @@ def _check(code: int, what: str):
 
 # --------------------------------------------------------------------------
 
-def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor):
-    """``out[t] = table[ids[t]]`` as float32.  ids int32 [T]; table [V, H]."""
+def embed(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: torch.Tensor, scale: float = 1.0):
+    """``out[t] = table[ids[t]] * scale`` as float32.  ids int32 [T]; table [V, H]."""
     _cuda(ids, table, out)
     assert ids.dtype == torch.int32 and out.dtype == torch.float32
     assert table.is_contiguous() and out.is_contiguous()
     T, (V, H) = ids.shape[0], table.shape
     assert out.shape == (T, H)
-    _check(lib().prism_embed(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, V, _ptr(err),
-                             _stream()), "embed")
+    _check(lib().prism_embed(_ptr(ids), _ptr(table), _dt(table), _ptr(out), T, H, V, float(scale),
+                             _ptr(err), _stream()), "embed")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
@@ -1109,3 +1116,202 @@ def feed_forward_swiglu(ctx, x: torch.Tensor, gate_up_w: torch.Tensor, down_w: t
     act = ctx.alloc((x.shape[0], gate_up_w.shape[0] // 2), x.dtype)
     swiglu(gu, act)
     return linear_delta(act, down_w)
+
+
+# --------------------------------------------------------------------------
+# attention with a key mask, a softmax sink and keys and values of different sizes
+# --------------------------------------------------------------------------
+
+MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2      # csrc/common.cuh: PRISM_MASK_*
+
+
+class KeyMask:
+    """Which keys a position sees; every kind is causal.  ``causal``: all keys
+    from 0; ``window(n)``: the last n (itself and the n - 1 before it);
+    ``chunk(n)``: those of its own block of n positions, blocks counted from
+    position 0 of the sequence."""
+
+    __slots__ = ("kind", "size")
+
+    def __init__(self, kind: int = MASK_CAUSAL, size: int = 0):
+        if kind not in (MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK):
+            raise ValueError(f"unknown mask kind {kind}")
+        if kind != MASK_CAUSAL and int(size) < 1:
+            raise ValueError(f"a window or chunk needs a size of at least 1, got {size}")
+        self.kind, self.size = int(kind), int(size) if kind != MASK_CAUSAL else 0
+
+    @classmethod
+    def causal(cls):
+        return cls()
+
+    @classmethod
+    def window(cls, n: Optional[int]):
+        return cls() if not n else cls(MASK_WINDOW, n)
+
+    @classmethod
+    def chunk(cls, n: Optional[int]):
+        return cls() if not n else cls(MASK_CHUNK, n)
+
+    def first_key(self, pos: int) -> int:
+        """The first key the token at ``pos`` sees (the last is ``pos`` itself)."""
+        if self.kind == MASK_WINDOW:
+            return max(0, pos - self.size + 1)
+        if self.kind == MASK_CHUNK:
+            return pos // self.size * self.size
+        return 0
+
+    def most_keys(self, max_kv_len: int) -> int:
+        return max_kv_len if self.kind == MASK_CAUSAL else min(max_kv_len, self.size)
+
+    def __repr__(self):
+        return f"KeyMask({('causal', 'window', 'chunk')[self.kind]}, {self.size})"
+
+
+def _plane_strides(plane: torch.Tensor):
+    """``(elements between consecutive slots, elements between kv heads)`` of a cache plane
+    ``[pages, P, nkv, d]`` (or a slice of its last axis); slots of a page and pages follow one another."""
+    assert plane.dim() == 4 and plane.stride(3) == 1 and plane.stride(0) == plane.shape[1] * plane.stride(1)
+    return plane.stride(1), plane.stride(2)
+
+
+def attention_masked_generic(q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                             block_table: torch.Tensor, positions: torch.Tensor, tok_seg: torch.Tensor,
+                             num_pages: int, mask: KeyMask, scale: float, sink: Optional[torch.Tensor],
+                             err: torch.Tensor):
+    """Shape-generic paged attention: ``q [T, nh, dk]`` (token and head strides free), keys ``[pages, P, nkv,
+    dk]``, values ``[pages, P, nkv, dv]`` (may be a slice of the key plane), ``out [T, nh * dv]``; ``sink
+    [nh]``: one more term ``exp(sink_h)`` in head h's softmax denominator.  float32 or bf16 storage, all
+    arithmetic float32."""
+    _cuda(q, out, k_plane, v_plane, block_table, positions, tok_seg, sink)
+    T, nh, dk = q.shape
+    P, nkv, dv = k_plane.shape[1], k_plane.shape[2], v_plane.shape[3]
+    assert k_plane.shape[3] == dk and v_plane.shape[:3] == k_plane.shape[:3]
+    assert q.stride(2) == 1 and out.stride(1) == 1 and out.shape == (T, nh * dv)
+    assert k_plane.dtype == q.dtype and v_plane.dtype == q.dtype and out.dtype == q.dtype
+    assert positions.dtype == torch.int32 and tok_seg.dtype == torch.int32 and block_table.dtype == torch.int32
+    krs, khs = _plane_strides(k_plane)
+    vrs, vhs = _plane_strides(v_plane)
+    if sink is not None:
+        assert sink.shape == (nh,) and sink.is_contiguous()
+    _check(lib().prism_attention_masked_generic(
+        _ptr(q), q.stride(0) if T > 1 else nh * dk, q.stride(1) if nh > 1 else dk, _ptr(out),
+        out.stride(0) if T > 1 else nh * dv, _ptr(k_plane), krs, khs, _ptr(v_plane), vrs, vhs, _dt(q),
+        _ptr(block_table), block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, nh, nkv, dk, dv, P, num_pages,
+        mask.kind, mask.size, float(scale), _ptr(sink), F32 if sink is None else _dt(sink), _ptr(err), _stream()),
+        "attention_masked_generic")
+
+
+def cache_store(src: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
+                tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor):
+    """Rows ``src [T, width]`` (row stride free) into the paged plane ``[pages, P, ...]`` (``width`` entries a
+    slot), each at its token's position."""
+    _cuda(src, plane, block_table, positions, tok_seg)
+    T, width = src.shape
+    P = plane.shape[1]
+    assert plane.is_contiguous() and plane[0, 0].numel() == width and plane.dtype == src.dtype and src.stride(1) == 1
+    _check(lib().prism_cache_store(_ptr(src), src.stride(0) if T > 1 else width, _ptr(plane), _dt(src), width,
+                                   _ptr(block_table), block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, P,
+                                   num_pages, int(max_pos), _ptr(err), _stream()), "cache_store")
+
+
+def latent_kv_store(x: torch.Tensor, weight: torch.Tensor, eps: float, rank: int, rot_dims: int,
+                    inv_freq: Optional[torch.Tensor], plane: torch.Tensor, block_table: torch.Tensor,
+                    positions: torch.Tensor, tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor):
+    """The cache row of latent attention from its down projection ``x [T, rank + r]`` (float32): the first
+    ``rank`` entries RMS-normed with ``weight``, the last ``r`` with their first ``rot_dims`` entries rotated
+    by the token's position; stored at the token's slot of ``plane [pages, P, 1, rank + r]``."""
+    _cuda(x, weight, inv_freq, plane, block_table, positions, tok_seg)
+    T, width = x.shape
+    r = width - rank
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and weight.shape == (rank,) and weight.is_contiguous()
+    assert plane.is_contiguous() and plane[0, 0].numel() == width
+    if rot_dims:
+        assert inv_freq.dtype == torch.float32 and inv_freq.shape[0] * 2 == rot_dims
+    _check(lib().prism_latent_kv_store(_ptr(x), x.stride(0) if T > 1 else width, _ptr(weight), _dt(weight), float(eps),
+                                       rank, r, int(rot_dims), _ptr(inv_freq), _ptr(plane), _dt(plane), _ptr(block_table),
+                                       block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, plane.shape[1], num_pages,
+                                       int(max_pos), _ptr(err), _stream()), "latent_kv_store")
+
+
+def rotate_slice(src: torch.Tensor, dst: torch.Tensor, rot_dims: int, inv_freq: Optional[torch.Tensor],
+                 positions: torch.Tensor):
+    """``dst[t, h, :] = src[t, h, :]`` with the first ``rot_dims`` entries rotated by token t's position (entry
+    i paired with i + rot_dims / 2).  ``src`` and ``dst`` are ``[T, nh, width]`` views with token and head
+    strides of their own."""
+    _cuda(src, dst, inv_freq, positions)
+    T, nh, width = src.shape
+    assert dst.shape == src.shape and dst.dtype == src.dtype and src.stride(2) == 1 and dst.stride(2) == 1
+    _check(lib().prism_rotate_slice(_ptr(src), src.stride(0), src.stride(1), _ptr(dst), dst.stride(0), dst.stride(1),
+                                    _dt(src), width, int(rot_dims), _ptr(inv_freq), _ptr(positions), T, nh, _stream()),
+           "rotate_slice")
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}      # csrc/activation.cu: PRISM_ACT_*
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str):
+    """``out = act(x)`` elementwise for ``[rows, cols]`` tensors with row strides of their own."""
+    _cuda(x, out)
+    rows, cols = x.shape
+    assert out.shape == x.shape and out.dtype == x.dtype and x.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().prism_activation(_ptr(x), x.stride(0), _ptr(out), out.stride(0), _dt(x), rows, cols,
+                                  ACTIVATIONS[kind], _stream()), "activation")
+
+
+def masked_attention(ctx, q: torch.Tensor, out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor,
+                     block_table: torch.Tensor, num_pages: int, mask: KeyMask, scale: float,
+                     sink: Optional[torch.Tensor] = None):
+    """Attention of the step's tokens over one cache plane whose keys and values may differ in size, under a
+    ``KeyMask`` and with an optional softmax sink.  The kernel is chosen by dtype and shape; the shape-generic
+    one takes what the tensor-core kernel refuses."""
+    attention_masked_generic(q, out, k_plane, v_plane, block_table, ctx.positions, ctx.tok_seg, num_pages, mask,
+                             scale, sink, ctx.err)
+
+
+def feed_forward_act(ctx, x: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, kind: str,
+                     up_b: Optional[torch.Tensor] = None, down_b: Optional[torch.Tensor] = None):
+    """``down(act(up(x)))``."""
+    hidden = linear(x, up_w, up_b)
+    act = ctx.alloc(hidden.shape, x.dtype)
+    activation(hidden, act, kind)
+    return linear_delta(act, down_w, down_b)
+
+
+def stack_deltas(ctx, deltas):
+    """Several results that are to be added to the residual stream together, as one float32 stack ``[k, T,
+    H]`` for the fused add + norm kernel.  Each is ``[T, H]`` in any dtype or already a float32 stack of
+    partial sums."""
+    parts = [d if d.dim() == 3 else d.unsqueeze(0) for d in deltas]
+    if all(p.dtype == torch.float32 for p in parts):
+        return torch.cat(parts, 0)
+    out = ctx.alloc((sum(p.shape[0] for p in parts),) + tuple(parts[0].shape[1:]), torch.float32)
+    o = 0
+    for p in parts:
+        out[o:o + p.shape[0]].copy_(p)
+        o += p.shape[0]
+    return out
+
+
+def rms_rows(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor):
+    """``out = x / sqrt(mean(x^2) + eps) * weight`` row by row; ``x [rows, width]`` float32 and ``out`` (the
+    compute dtype) with row strides of their own."""
+    _cuda(x, weight, out)
+    rows, width = x.shape
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and out.stride(1) == 1 and out.shape == x.shape
+    assert weight.shape == (width,) and weight.is_contiguous()
+    _check(lib().prism_rms_rows(_ptr(x), x.stride(0), _ptr(weight), _dt(weight), float(eps), _ptr(out), out.stride(0),
+                                _dt(out), rows, width, _stream()), "rms_rows")
+
+
+def matmul_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
+    """Per head h: ``out[:, h, :] = x[:, h, :] @ w[h].T`` for ``x [T, H, K]``, ``w [H, N, K]`` and ``out [T, H,
+    N]`` (views with token and head strides of their own, last axis dense).  float32: the true-float32 kernel
+    head by head; bf16: the library's batched product with float32 accumulation."""
+    _cuda(x, w, out)
+    T, H, K = x.shape
+    assert w.shape[0] == H and w.shape[2] == K and out.shape == (T, H, w.shape[1])
+    if x.dtype == torch.float32:
+        for h in range(H):
+            sgemm(x[:, h], w[h], None, out[:, h])
+        return
+    torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))

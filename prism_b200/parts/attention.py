@@ -3,7 +3,11 @@
 encoding of q and k, append of k and v to the paged cache, causal
 grouped-query attention over the cache with scale ``hd^-1/2``, output
 projection.  Head counts, head size, bias, window and the position encoding
-are parameters."""
+are parameters; so are a value size of its own, a chunked mask, a softmax
+sink, the score scale and whether the layer has key and value projections at
+all (a layer without reads another layer's cache plane).
+``latent_attention``: keys and values are up-projections of a low-rank latent
+that is all the cache holds, next to one rotated key part shared by the heads."""
 
 from __future__ import annotations
 
@@ -23,9 +27,23 @@ MAX_HEAD_DIM = 256        # the shape-generic attention kernel keeps one head's 
 
 @register_part("mixer", "gqa_attention")
 class GQAAttention(Mixer):
+    """``v_head_dim``: size of a value (default: ``head_dim``).  ``chunk``: a query sees only the keys of
+    its own block of ``chunk`` positions, counted from position 0 (with ``window``: both limits hold; the
+    fast kernels take one of the two).  ``sink``: a learned number per head whose exponential joins the
+    softmax's denominator, unscaled and without a value.  ``own_kv`` False: no key and value projections;
+    the layer's run must read another run's cache plane (``ScheduleEntry.reads_cache_of``).
+    ``cache_chunk``: the block size by which the cache gives pages back - ``"mask"``: that of this layer's
+    mask; None: never (a plane that layers with different masks read).  ``names``: the tensors' names in
+    the model file (keys q, k, v, o, q_b, k_b, v_b, o_b, sink)."""
+
+    NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight",
+                 q_b="q_proj.bias", k_b="k_proj.bias", v_b="v_proj.bias", o_b="o_proj.bias", sink="sinks")
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool = True, o_bias: bool = False, window: Optional[int] = None,
-                 position: Optional[PartSpec] = None, scale: Optional[float] = None):
+                 position: Optional[PartSpec] = None, scale: Optional[float] = None,
+                 v_head_dim: Optional[int] = None, chunk: Optional[int] = None, sink: bool = False,
+                 own_kv: bool = True, cache_chunk="mask", names: Optional[dict] = None):
         if num_heads % num_kv_heads:
             raise ConfigError(f"num_heads {num_heads} not divisible by num_kv_heads {num_kv_heads}")
         if not 2 <= int(head_dim) <= MAX_HEAD_DIM or int(head_dim) % 2:
@@ -36,6 +54,19 @@ class GQAAttention(Mixer):
         self.window = None if window is None else int(window)
         self.scale = float(scale) if scale is not None else self.hd ** -0.5
         self.position = self.add_child("position", build_part("position", position)) if position else None
+        self.vhd = self.hd if v_head_dim is None else int(v_head_dim)
+        self.chunk = None if chunk is None else int(chunk)
+        if self.vhd < 1 or (self.chunk is not None and self.chunk < 1) or (self.window is not None and self.window < 1):
+            raise ConfigError(f"value size {self.vhd}, chunk {self.chunk}, window {self.window}: all must be at least 1")
+        if self.chunk is not None and self.window is not None:
+            raise ConfigError("a layer's mask is a window or a chunk, not both")
+        self.sink, self.own_kv = bool(sink), bool(own_kv)
+        self.cache_chunk = self.chunk if cache_chunk == "mask" else (None if cache_chunk is None else int(cache_chunk))
+        self.names = dict(self.NAMES, **(names or {}))
+        # what the fused rotate-and-store and the equal-size attention kernels do not cover goes the general way:
+        # projection, (rotation,) one store per plane, attention under a KeyMask
+        self.general = self.vhd != self.hd or self.chunk is not None or self.sink or not self.own_kv
+        self.mask = ops.KeyMask.chunk(self.chunk) if self.chunk is not None else ops.KeyMask.window(self.window)
 
     @property
     def q_size(self):
@@ -45,27 +76,37 @@ class GQAAttention(Mixer):
     def kv_size(self):
         return self.nkv * self.hd
 
+    @property
+    def v_size(self):
+        return self.nkv * self.vhd
+
     def cache_need(self):
-        return CacheNeed("paged", self.nkv, self.hd, self.window)
+        return CacheNeed("paged", self.nkv, self.hd, self.window,
+                         v_head_dim=None if self.vhd == self.hd else self.vhd, chunk=self.cache_chunk)
 
     def params(self):
-        H, qs, kvs = self.hidden_size, self.q_size, self.kv_size
-        ps = [ParamSpec("qkv_w", (WeightSource("q_proj.weight", (qs, H)),
-                                  WeightSource("k_proj.weight", (kvs, H)),
-                                  WeightSource("v_proj.weight", (kvs, H))))]
+        H, qs, kvs, vs, n = self.hidden_size, self.q_size, self.kv_size, self.v_size, self.names
+        w = [WeightSource(n["q"], (qs, H))]
+        b = [WeightSource(n["q_b"], (qs,), "bias")]
+        if self.own_kv:
+            w += [WeightSource(n["k"], (kvs, H)), WeightSource(n["v"], (vs, H))]
+            b += [WeightSource(n["k_b"], (kvs,), "bias"), WeightSource(n["v_b"], (vs,), "bias")]
+        ps = [ParamSpec("qkv_w", tuple(w))]
         if self.qkv_bias:
-            ps.append(ParamSpec("qkv_b", (WeightSource("q_proj.bias", (qs,), "bias"),
-                                          WeightSource("k_proj.bias", (kvs,), "bias"),
-                                          WeightSource("v_proj.bias", (kvs,), "bias"))))
-        ps.append(ParamSpec("o_w", (WeightSource("o_proj.weight", (H, qs)),)))
+            ps.append(ParamSpec("qkv_b", tuple(b)))
+        if self.sink:
+            ps.append(ParamSpec("sink", (WeightSource(n["sink"], (self.nh,), "bias"),)))
+        ps.append(ParamSpec("o_w", (WeightSource(n["o"], (H, self.nh * self.vhd)),)))
         if self.o_bias:
-            ps.append(ParamSpec("o_b", (WeightSource("o_proj.bias", (H,), "bias"),)))
+            ps.append(ParamSpec("o_b", (WeightSource(n["o_b"], (H,), "bias"),)))
         return ps
 
     def on_bound(self):
         # Said once, when the model is built, not found out from the step time: in bfloat16 the tensor-core
         # attention kernels take head sizes in steps of 16 up to 128 with up to 16 query heads per kv head; every
         # other shape runs on the shape-generic kernel (one warp per token and head), correct but far slower.
+        if self.general:
+            return
         if self.dtype == torch.bfloat16 and not ops.attention_bf16_shape_ok(self.hd, self.nh, self.nkv):
             key = (self.hd, self.nh, self.nkv)
             if key not in _warned:
@@ -75,7 +116,37 @@ class GQAAttention(Mixer):
                               f"and up to 16 query heads per kv head): correct, but much slower", RuntimeWarning,
                               stacklevel=2)
 
+    def _forward_general(self, ctx, x, cache):
+        """Projection (+ bias), rotation if the layer has one, one store per cache plane, attention under the
+        layer's mask with its sink, output projection."""
+        T, qs, kvs = x.shape[0], self.q_size, self.kv_size
+        if cache.write != self.own_kv:
+            raise ValueError("a layer without key and value projections must read another run's cache plane, "
+                             "and one with them owns its plane")
+        qkv = ops.linear(x, self.w["qkv_w"], self.w.get("qkv_b"))
+        q = qkv[:, :qs].view(T, self.nh, self.hd)
+        k = qkv[:, qs:qs + kvs].view(T, self.nkv, self.hd) if self.own_kv else None
+        if self.position is not None:
+            rot = self.position.rotary()
+            if rot is None:
+                self.position.apply(ctx, q, k)
+            elif rot.rotary_dim:
+                ops.rotate_slice(q, q, rot.rotary_dim, rot.inv_freq, ctx.positions)
+                if k is not None:
+                    ops.rotate_slice(k, k, rot.rotary_dim, rot.inv_freq, ctx.positions)
+        if self.own_kv:
+            ops.cache_store(qkv[:, qs:qs + kvs], cache.k, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages,
+                            ctx.max_positions, ctx.err)
+            ops.cache_store(qkv[:, qs + kvs:], cache.v, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages,
+                            ctx.max_positions, ctx.err)
+        attn = ctx.alloc((T, self.nh * self.vhd), x.dtype)
+        ops.masked_attention(ctx, q, attn, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
+                             self.w.get("sink"))
+        return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))
+
     def forward(self, ctx, x, cache):
+        if self.general:
+            return self._forward_general(ctx, x, cache)
         T, qs, kvs = x.shape[0], self.q_size, self.kv_size
         rot = self.position.rotary() if self.position is not None else None
         if rot is None and self.position is not None:
@@ -96,3 +167,92 @@ class GQAAttention(Mixer):
         attn = ctx.alloc((T, qs), x.dtype)
         ops.attention(ctx, q, attn, cache, self.window, self.scale)
         return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))
+
+
+@register_part("mixer", "latent_attention")
+class LatentAttention(Mixer):
+    """Attention whose keys and values are up-projections of a cached latent.
+
+    With h the layer's input, per token::
+
+        c_q = rmsnorm(W_dq h)            q = W_uq c_q        per head [head_dim plain | rot_dim rotated]
+        [c' | k_r] = W_dkv h             c = rmsnorm(c')     k_r: rot_dim entries, rotated, one for all heads
+        k_h = W_uk,h c                   v_h = W_uv,h c
+        score_h(i, j) = (q_plain,h(i) . k_h(j) + q_rot,h(i) . k_r(j)) * scale
+
+    The cache holds ``[c | k_r]`` per token (``kv_rank + rot_dim`` numbers, one "head").  Nothing is
+    up-projected again at a later step: the key up-projection moves to the query side (``q_plain,h W_uk,h``
+    is scored against c itself) and the value up-projection behind the attention (the weighted sum of the
+    latents is projected once per query), so each step is attention with ``num_heads`` query heads over one
+    key/value head whose values are the first ``kv_rank`` entries of its key rows.
+
+    ``window``: sliding window (None: all keys).  ``rope_dims`` (default ``rot_dim``): how many entries of the
+    rotated part really turn.  ``names``: the tensors' names in the model file.
+    """
+
+    NAMES = dict(dq="q_a_proj.weight", dq_norm="q_a_layernorm.weight", uq="q_b_proj.weight",
+                 dkv="kv_a_proj_with_mqa.weight", dkv_norm="kv_a_layernorm.weight", uk="k_b_proj.weight",
+                 uv="v_b_proj.weight", o="o_proj.weight")
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int, q_rank: int,
+                 kv_rank: int, eps: float, rope_base: float = 10000.0, rope_dims: Optional[int] = None,
+                 window: Optional[int] = None, scale: Optional[float] = None, names: Optional[dict] = None):
+        self.hidden_size, self.nh, self.hd = int(hidden_size), int(num_heads), int(head_dim)
+        self.rd, self.vhd, self.q_rank, self.kv_rank = int(rot_dim), int(v_head_dim), int(q_rank), int(kv_rank)
+        self.eps, self.rope_base = float(eps), float(rope_base)
+        self.rope_dims = self.rd if rope_dims is None else int(rope_dims)
+        if self.rope_dims % 2 or not 0 <= self.rope_dims <= self.rd:
+            raise ConfigError(f"{self.rope_dims} rotated entries: must be even and at most rot_dim {self.rd}")
+        if min(self.nh, self.hd, self.vhd, self.q_rank, self.kv_rank) < 1 or self.rd < 0:
+            raise ConfigError("latent attention: heads, sizes and ranks must be positive")
+        self.window = None if window is None else int(window)
+        if self.window is not None and self.window < 1:
+            raise ConfigError(f"window {self.window} must be at least 1")
+        self.scale = float(scale) if scale is not None else (self.hd + self.rd) ** -0.5
+        self.names = dict(self.NAMES, **(names or {}))
+        self.mask = ops.KeyMask.window(self.window)
+
+    def cache_need(self):
+        return CacheNeed("paged", 1, self.kv_rank + self.rd, self.window, v_head_dim=0)
+
+    def params(self):
+        H, nh, n = self.hidden_size, self.nh, self.names
+        return [
+            ParamSpec("down_w", (WeightSource(n["dq"], (self.q_rank, H)),
+                                 WeightSource(n["dkv"], (self.kv_rank + self.rd, H)))),
+            ParamSpec("dq_norm", (WeightSource(n["dq_norm"], (self.q_rank,), "norm"),)),
+            ParamSpec("dkv_norm", (WeightSource(n["dkv_norm"], (self.kv_rank,), "norm"),)),
+            ParamSpec("uq_w", (WeightSource(n["uq"], (nh * (self.hd + self.rd), self.q_rank)),)),
+            ParamSpec("uk_w", (WeightSource(n["uk"], (nh * self.hd, self.kv_rank)),)),
+            ParamSpec("uv_w", (WeightSource(n["uv"], (nh * self.vhd, self.kv_rank)),)),
+            ParamSpec("o_w", (WeightSource(n["o"], (H, nh * self.vhd)),)),
+        ]
+
+    def on_bound(self):
+        half = self.rope_dims // 2
+        i = torch.arange(half, dtype=torch.float64)
+        self.inv_freq = (self.rope_base ** (-2.0 * i / max(self.rope_dims, 1))).to(torch.float32).to(self.device)
+        # W_uk per head, turned so that a head's plain query part is projected into the latent space
+        self.uk_t = self.w["uk_w"].view(self.nh, self.hd, self.kv_rank).transpose(1, 2).contiguous()     # [nh, R, hd]
+        self.uv = self.w["uv_w"].view(self.nh, self.vhd, self.kv_rank)                                  # [nh, vhd, R]
+
+    def forward(self, ctx, x, cache):
+        T, nh, hd, rd, R = x.shape[0], self.nh, self.hd, self.rd, self.kv_rank
+        # both down projections in one product; float32, because each feeds a norm
+        down = ops.linear(x, self.w["down_w"], None, out_dtype=torch.float32)
+        cq = ctx.alloc((T, self.q_rank), x.dtype)
+        ops.rms_rows(down[:, :self.q_rank], self.w["dq_norm"], self.eps, cq)
+        ops.latent_kv_store(down[:, self.q_rank:], self.w["dkv_norm"], self.eps, R, self.rope_dims, self.inv_freq,
+                            cache.k, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages, ctx.max_positions,
+                            ctx.err)
+        q = ops.linear(cq, self.w["uq_w"]).view(T, nh, hd + rd)
+        qf = ctx.alloc((T, nh, R + rd), x.dtype)                   # per head [plain part in latent space | rotated part]
+        ops.matmul_heads(q[:, :, :hd], self.uk_t, qf[:, :, :R])
+        if rd:
+            ops.rotate_slice(q[:, :, hd:], qf[:, :, R:], self.rope_dims, self.inv_freq, ctx.positions)
+        lat = ctx.alloc((T, nh * R), x.dtype)
+        ops.masked_attention(ctx, qf, lat, cache.k, cache.k[..., :R], cache.block_table, cache.num_pages, self.mask,
+                             self.scale, None)
+        attn = ctx.alloc((T, nh * self.vhd), x.dtype)
+        ops.matmul_heads(lat.view(T, nh, R), self.uv, attn.view(T, nh, self.vhd))
+        return ops.linear_delta(attn, self.w["o_w"])

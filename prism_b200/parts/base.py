@@ -69,7 +69,11 @@ class ParamSpec:
 class CacheNeed:
     """``paged``: keys and values of ``num_kv_heads x head_dim`` per token in
     pages; ``window`` None keeps every key, an integer keeps the last
-    ``window`` positions (older pages are given back).  ``state``: one tensor
+    ``window`` positions (older pages are given back); ``chunk``: queries see
+    only the keys of their own block of ``chunk`` positions (counted from 0),
+    so the pages of earlier blocks are given back.  ``v_head_dim``: size of a
+    value when it differs from a key's (None: the same; 0: no value plane at
+    all, the values are read out of the key rows).  ``state``: one tensor
     of ``state_shape`` per request, in a slot.  ``none``: nothing."""
     kind: str = "none"
     num_kv_heads: int = 0
@@ -77,10 +81,26 @@ class CacheNeed:
     window: Optional[int] = None
     state_shape: Tuple[int, ...] = ()
     state_dtype: str = "float32"
+    v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else int(self.v_head_dim)
+
+    def first_kept(self, length: int) -> int:
+        """The first position that the query at position ``length`` (the next one of a request holding
+        ``length`` tokens) can still see; everything before it may be given back."""
+        lo = 0
+        if self.window is not None:
+            lo = max(lo, length - self.window + 1)
+        if self.chunk is not None:
+            lo = max(lo, length // self.chunk * self.chunk)
+        return lo
 
     def group_key(self):
         return (self.kind, self.num_kv_heads, self.head_dim, self.window,
-                tuple(self.state_shape), self.state_dtype)
+                tuple(self.state_shape), self.state_dtype, self.value_dim, self.chunk)
 
 
 @dataclass

@@ -8,18 +8,21 @@ from .. import ops
 
 @register_part("embedding", "token")
 class TokenEmbedding(Embedding):
-    """Row gather without scaling; the output is the float32 residual stream."""
+    """Row gather, times ``scale`` (in float32; 1: no scaling); the output is the
+    float32 residual stream.  ``tensor``: the table's name in the model file."""
 
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, tensor: str = "embed_tokens.weight"):
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
+        self.scale = float(scale)
+        self.tensor = tensor
 
     def params(self):
-        return [ParamSpec("weight", (WeightSource("embed_tokens.weight", (self.vocab_size, self.hidden_size)),))]
+        return [ParamSpec("weight", (WeightSource(self.tensor, (self.vocab_size, self.hidden_size)),))]
 
     def forward(self, ctx):
         out = ctx.alloc((ctx.T, self.hidden_size), ops.torch.float32)
-        ops.embed(ctx.token_ids, self.w["weight"], out, ctx.err)
+        ops.embed(ctx.token_ids, self.w["weight"], out, ctx.err, self.scale)
         return out
 
 
@@ -30,13 +33,14 @@ class LinearHead(Head):
     head tensor (engine/weight_manager.py:84-86; the reference copies into a
     second buffer, engine/weight_pool.py:157-160: here it is one buffer)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str = None):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str = None, tensor: str = "weight"):
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.tied_to = tied_to
+        self.tensor = tensor
 
     def params(self):
-        return [ParamSpec("weight", (WeightSource("weight", (self.vocab_size, self.hidden_size)),),
+        return [ParamSpec("weight", (WeightSource(self.tensor, (self.vocab_size, self.hidden_size)),),
                           optional=self.tied_to is not None, absent="none", alias_of=self.tied_to)]
 
     def forward(self, ctx, normed_rows):

@@ -1,6 +1,7 @@
 """Feed-forward parts.  ``swiglu``: andre-fu/prism's dense MLP
 (engine/executor.py:125-127): fused gate/up projection, ``silu(gate) * up``,
-down projection; no biases (engine/weight_pool.py:194-199)."""
+down projection; no biases (engine/weight_pool.py:194-199).  ``mlp``: up
+projection, an elementwise activation, down projection."""
 
 from __future__ import annotations
 
@@ -24,3 +25,26 @@ class SwiGLU(FeedForward):
 
     def forward(self, ctx, x):
         return ops.feed_forward_swiglu(ctx, x, self.w["gate_up_w"], self.w["down_w"])
+
+
+@register_part("feed_forward", "mlp")
+class ActMLP(FeedForward):
+    """``down(act(up(x)))`` without gate.  ``activation``: one of ``ops.ACTIVATIONS`` (``relu2``: the square of
+    relu; ``gelu_tanh``; ``silu``; ``relu``).  ``names``: the up and down tensors' names in the model file."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu2",
+                 names=("up_proj.weight", "down_proj.weight")):
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {activation!r}: one of {sorted(ops.ACTIVATIONS)}")
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        self.activation = activation
+        self.names = tuple(names)
+
+    def params(self):
+        H, I = self.hidden_size, self.intermediate_size
+        return [ParamSpec("up_w", (WeightSource(self.names[0], (I, H)),)),
+                ParamSpec("down_w", (WeightSource(self.names[1], (H, I)),))]
+
+    def forward(self, ctx, x):
+        return ops.feed_forward_act(ctx, x, self.w["up_w"], self.w["down_w"], self.activation)

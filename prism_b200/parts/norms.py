@@ -13,12 +13,13 @@ class RMSNorm(Norm):
     """``x * rsqrt(mean(x^2) + eps) * weight``: the weight multiplies (no
     ``1 + w``), no bias, no mean subtraction (fused_kernels.py:41-49)."""
 
-    def __init__(self, width: int, eps: float):
+    def __init__(self, width: int, eps: float, tensor: str = "weight"):
         self.width = int(width)
         self.eps = float(eps)
+        self.tensor = tensor          # the weight's name in the model file, after the part's prefix
 
     def params(self):
-        return [ParamSpec("weight", (WeightSource("weight", (self.width,), "norm"),))]
+        return [ParamSpec("weight", (WeightSource(self.tensor, (self.width,), "norm"),))]
 
     def forward(self, ctx, residual, delta, rows=None):
         n = residual.shape[0] if rows is None else rows.shape[0]
