@@ -92,6 +92,9 @@ class _Sig:
                                _i, _f, _p, _p]
     prism_attention_masked_generic = [_p, _i, _i, _p, _i, _p, _ll, _i, _p, _ll, _i, _i, _p, _i, _p, _p, _i, _i, _i,
                                       _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _p]
+    prism_attention_masked_supported = [_i, _i, _i, _i]
+    prism_attention_masked_bf16 = [_p, _ll, _i, _p, _ll, _p, _ll, _i, _p, _ll, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
+                                   _i, _i, _i, _i, _f, _p, _i, _i, _p, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_rotate_slice = [_p, _ll, _i, _p, _ll, _i, _i, _i, _i, _p, _p, _i, _i, _p]
@@ -1264,8 +1267,59 @@ def masked_attention(ctx, q: torch.Tensor, out: torch.Tensor, k_plane: torch.Ten
     """Attention of the step's tokens over one cache plane whose keys and values may differ in size, under a
     ``KeyMask`` and with an optional softmax sink.  The kernel is chosen by dtype and shape; the shape-generic
     one takes what the tensor-core kernel refuses."""
+    T, nh, dk = q.shape
+    nkv, dv = k_plane.shape[2], v_plane.shape[3]
+    if (q.dtype == torch.bfloat16 and MASKED_TC and not FORCE_GENERIC_ATTENTION
+            and attention_masked_tc_ok(q, k_plane, v_plane, nh, nkv, dk, dv)):
+        few = ctx.decode_only and nh // nkv <= 16
+        attention_masked_bf16(q, out, k_plane, v_plane, block_table, ctx.seg_start, ctx.cached_len, ctx.S,
+                              ctx.max_q_len, num_pages, mask, scale, sink, few, ctx.err)
+        return
     attention_masked_generic(q, out, k_plane, v_plane, block_table, ctx.positions, ctx.tok_seg, num_pages, mask,
                              scale, sink, ctx.err)
+
+
+MASKED_TC = os.environ.get("PRISM_MASKED_TC", "1") != "0"
+
+
+def _values_in_keys(k_plane: torch.Tensor, v_plane: torch.Tensor) -> bool:
+    """Whether the values are the leading entries of the key rows (one plane, read once)."""
+    return v_plane.data_ptr() == k_plane.data_ptr() and v_plane.stride()[:3] == k_plane.stride()[:3]
+
+
+def attention_masked_tc_ok(q, k_plane, v_plane, nh: int, nkv: int, dk: int, dv: int) -> bool:
+    """The rule of ``prism_attention_masked_bf16`` (csrc/attention_masked.cu): whole 16-byte pieces everywhere,
+    values of up to 256 entries."""
+    if not lib().prism_attention_masked_supported(dk, dv, nh, nkv):
+        return False
+    krs, khs = _plane_strides(k_plane)
+    ok = (q.stride(0) % 8 == 0 or q.shape[0] == 1) and (q.stride(1) % 8 == 0 or nh == 1) and q.data_ptr() % 16 == 0 \
+        and krs % 8 == 0 and khs % 8 == 0 and k_plane.data_ptr() % 16 == 0
+    if _values_in_keys(k_plane, v_plane):
+        return ok and dv <= dk
+    vrs, vhs = _plane_strides(v_plane)
+    return ok and dv % 8 == 0 and vrs % 8 == 0 and vhs % 8 == 0 and v_plane.data_ptr() % 16 == 0
+
+
+def attention_masked_bf16(q, out, k_plane, v_plane, block_table, seg_start, cached_len, S: int, max_q_len: int,
+                          num_pages: int, mask: KeyMask, scale: float, sink: Optional[torch.Tensor], few_rows: bool,
+                          err: torch.Tensor):
+    """Tensor-core attention under a ``KeyMask`` with an optional sink; ``few_rows``: a decode step (one token
+    per segment, at most 16 query heads per kv head), where a CTA's four warps share the keys."""
+    _cuda(q, out, k_plane, v_plane, block_table, seg_start, cached_len, sink)
+    T, nh, dk = q.shape
+    P, nkv, dv = k_plane.shape[1], k_plane.shape[2], v_plane.shape[3]
+    assert q.dtype == torch.bfloat16 and k_plane.dtype == torch.bfloat16 and out.dtype == torch.bfloat16
+    assert q.stride(2) == 1 and out.stride(1) == 1 and out.shape == (T, nh * dv) and seg_start.shape[0] == S + 1
+    krs, khs = _plane_strides(k_plane)
+    vrs, vhs = _plane_strides(v_plane)
+    vin = _values_in_keys(k_plane, v_plane)
+    _check(lib().prism_attention_masked_bf16(
+        _ptr(q), q.stride(0) if T > 1 else nh * dk, q.stride(1) if nh > 1 else dk, _ptr(out),
+        out.stride(0) if T > 1 else nh * dv, _ptr(k_plane), krs, khs, None if vin else _ptr(v_plane), vrs, vhs,
+        _ptr(block_table), block_table.shape[1], _ptr(seg_start), _ptr(cached_len), S, int(max_q_len), nh, nkv, dk, dv,
+        P, num_pages, mask.kind, mask.size, float(scale), _ptr(sink), F32 if sink is None else _dt(sink),
+        1 if few_rows else 0, _ptr(err), _stream()), "attention_masked_bf16")
 
 
 def feed_forward_act(ctx, x: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, kind: str,
