@@ -1,0 +1,257 @@
+"""Prefill and decode throughput of the Dolezen design at layer sizes that resemble real models (random
+weights, bf16), beside the Qwen2 architecture at equal width, depth and parameter count, and the attention
+kernels of both on the same problem with their fractions of the measured peaks.
+
+    python bench.py --design dolezen [--sizes 2k,4k] [--steps K] [--warmup W]
+    python benchmarks/design_bench.py [--sizes 2k] [--kernels-only] [--once KERNEL]
+
+One JSON line.  Timing: CUDA events after W >= 3 warm-up runs; every timed step reads all weights (more than
+the 126 MB L2) and the kernel timings flush L2 between launches.
+"""
+
+import argparse
+import json
+import os
+import sys
+import time
+import types
+
+import torch
+
+ROOT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..")
+sys.path.insert(0, ROOT)
+
+DEV = "cuda:0"
+PAGE = 64
+# width, feed-forward, heads / kv heads / key size / value size of the chunked layers, and of the latent layers
+# heads / plain size / rotated size / value size / query rank / latent rank; mask sizes
+SIZES = {
+    "2k": dict(width=2048, ff=8192, heads=16, kv_heads=4, dim=128, vdim=128, lat_heads=16, lat_dim=128, rot=64,
+               lat_vdim=128, q_rank=768, kv_rank=192, chunk=1024, window=512, layers=8, vocab=32768),
+    "4k": dict(width=4096, ff=14336, heads=32, kv_heads=8, dim=128, vdim=128, lat_heads=32, lat_dim=128, rot=64,
+               lat_vdim=128, q_rank=1536, kv_rank=192, chunk=1024, window=512, layers=8, vocab=32768),
+}
+
+
+def dolezen_config(s):
+    att = dict(heads=s["heads"], kv_heads=s["kv_heads"], dim=s["dim"], vdim=s["vdim"], mask=dict(size=s["chunk"]),
+               scale=s["dim"] ** -0.5)
+    lat = dict(heads=s["lat_heads"], dim=s["lat_dim"], rot_dim=s["rot"], vdim=s["lat_vdim"], q_rank=s["q_rank"],
+               kv_rank=s["kv_rank"], mask=dict(size=s["window"]), rot=dict(base=10000.0, dims=s["rot"]),
+               scale=(s["lat_dim"] + s["rot"]) ** -0.5)
+    mlp = dict(kind="dense", ff=s["ff"])
+    layers = []
+    for i in range(s["layers"]):          # own keys, shared keys, latent, own keys, ...
+        k = i % 4
+        if k == 2:
+            layers.append(dict(type="latent_attention", mixer=dict(lat), mlp=mlp))
+        elif k == 1:
+            layers.append(dict(type="attention", mixer=dict(att, kv_from=i - 1), mlp=mlp))
+        else:
+            layers.append(dict(type="attention", mixer=dict(att), mlp=mlp))
+    return dict(architecture="Dolezen", vocab=s["vocab"], width=s["width"], norm=dict(eps=1e-6),
+                embedding=dict(scale=1.0), layers=layers, max_positions=8192)
+
+
+def qwen2_config(s):
+    # the same width, depth and head shape; a gated feed-forward has three matrices where the dense one has two
+    return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=s["layers"],
+                hidden_size=s["width"], num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"],
+                head_dim=s["dim"], intermediate_size=s["ff"] * 2 // 3 // 256 * 256, vocab_size=s["vocab"],
+                rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=8192,
+                use_sliding_window=False)
+
+
+def timeit(fn, reps=10, flush=True, warmup=3):
+    junk = torch.empty(256 << 20, dtype=torch.uint8, device=DEV) if flush else None
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(reps):
+        if flush:
+            junk.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / reps       # ms
+
+
+def engine_numbers(raw, prompt_len, batch, steps, warmup):
+    """Prefill tokens/s (one prompt of ``prompt_len`` tokens a step) and decode tokens/s (``batch`` requests
+    behind ``prompt_len`` tokens each, CUDA graphs) through the engine's step function."""
+    from prism_b200 import Engine, EngineConfig, SchedulerConfig, ops
+    from prism_b200.engine.batch import Segment
+    ctx_len = prompt_len + steps + warmup + 8
+    pages = (ctx_len + PAGE - 1) // PAGE
+    ec = EngineConfig(kv_page_size=PAGE, num_pages=(batch + 1) * pages + 8, max_seq_len=pages * PAGE, use_cuda_graph=True,
+                      graph_batch_sizes=(batch,),
+                      scheduler=SchedulerConfig(max_batch_tokens=prompt_len, max_num_seqs=batch + 1, prefill_chunk=prompt_len))
+    eng = Engine(None, ec, dtype="bfloat16", config=raw, random_seed=0)
+    runner = eng.runner
+    g = torch.Generator().manual_seed(1)
+    V = eng.model.spec.vocab_size
+    prompt = lambda: torch.randint(0, V, (prompt_len,), generator=g).tolist()
+    n = [0]
+
+    def prefill_once():
+        rid = f"p{n[0]}"
+        n[0] += 1
+        runner.begin_request(rid)
+        runner.step([Segment(rid, prompt(), [prompt_len - 1])])
+        runner.end_request(rid)
+    l0 = ops.launch_count
+    pre_ms = timeit(prefill_once, reps=max(3, min(steps, 8)), flush=False, warmup=max(3, warmup))
+    ids = [f"d{i}" for i in range(batch)]
+    for rid in ids:
+        runner.begin_request(rid)
+        runner.step([Segment(rid, prompt(), [])])
+    out = torch.empty(batch, dtype=torch.int32, device=DEV)
+
+    def decode_once():
+        logits = runner.step([Segment(rid, [1], [0]) for rid in ids])
+        ops.sample(logits, None, None, out)
+    for _ in range(max(3, warmup)):
+        decode_once()
+    torch.cuda.synchronize()
+    g0 = runner.graph_kernel_launches
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        decode_once()
+    e1.record()
+    torch.cuda.synchronize()
+    dec_ms = e0.elapsed_time(e1) / steps
+    runner.check_errors()
+    res = dict(prefill_tokens_per_s=round(prompt_len / pre_ms * 1e3), prefill_ms=round(pre_ms, 3),
+               decode_tokens_per_s=round(batch / dec_ms * 1e3), decode_ms_per_step=round(dec_ms, 4),
+               weights_gb=round(eng.pool.total_gb, 3), launches_per_decode_step=(runner.graph_kernel_launches - g0) // steps,
+               launches=ops.launch_count - l0 + runner.graph_kernel_launches - g0)
+    del eng, runner
+    torch.cuda.empty_cache()
+    return res
+
+
+def paged(batch, ctx, q_len, nkv, dk, dv, values_in_keys=False):
+    pages_per = (ctx + q_len + PAGE - 1) // PAGE
+    n_pages = batch * pages_per + 1
+    kc = torch.randn(n_pages, PAGE, nkv, dk, device=DEV, dtype=torch.bfloat16)
+    vc = kc[..., :dv] if values_in_keys else torch.randn(n_pages, PAGE, nkv, dv, device=DEV, dtype=torch.bfloat16)
+    bt = torch.arange(batch * pages_per, dtype=torch.int32, device=DEV).view(batch, pages_per)
+    i32 = lambda x: x.to(torch.int32).to(DEV)
+    ctx_ns = types.SimpleNamespace(
+        positions=i32(torch.cat([torch.arange(ctx, ctx + q_len) for _ in range(batch)])),
+        tok_seg=i32(torch.arange(batch).repeat_interleave(q_len)), seg_start=i32(torch.arange(batch + 1) * q_len),
+        cached_len=torch.full((batch,), ctx, dtype=torch.int32, device=DEV), S=batch, max_q_len=q_len,
+        decode_only=q_len == 1, err=torch.zeros(1, dtype=torch.int32, device=DEV))
+    return ctx_ns, kc, vc, bt, n_pages
+
+
+def visible_pairs(T0, n, mask):
+    return sum(p - mask.first_key(p) + 1 for p in range(T0, T0 + n))
+
+
+def kernel_numbers(s, pk, once=None):
+    """The attention kernels alone: Dolezen's chunked and latent layers against Qwen2's causal layer of the same
+    head shape, prefill of 2,048 tokens and a decode step of 8 and 64 requests behind 2,047 tokens."""
+    from prism_b200 import ops
+    out = {}
+    T = 2048
+    cases = [("chunked_sink", s["heads"], s["kv_heads"], s["dim"], s["vdim"], False, ops.KeyMask.chunk(s["chunk"]), True),
+             ("latent", s["lat_heads"], 1, s["kv_rank"] + s["rot"], s["kv_rank"], True, ops.KeyMask.window(s["window"]), False)]
+    for name, nh, nkv, dk, dv, vin, mask, sink in cases:
+        sk = torch.randn(nh, device=DEV) if sink else None
+        for label, batch, cached, q_len in (("prefill_2048", 1, 0, T), ("decode_b8", 8, T - 1, 1), ("decode_b64", 64, T - 1, 1)):
+            if once and once != f"{name}_{label}":
+                continue
+            c, kc, vc, bt, npages = paged(batch, cached, q_len, nkv, dk, dv, vin)
+            q = torch.randn(batch * q_len, nh, dk, device=DEV, dtype=torch.bfloat16)
+            o = torch.empty(batch * q_len, nh * dv, device=DEV, dtype=torch.bfloat16)
+            fn = lambda: ops.masked_attention(c, q, o, kc, vc, bt, npages, mask, dk ** -0.5, sk)
+            if once:
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                return {}
+            ms = timeit(fn)
+            pairs = batch * visible_pairs(cached, q_len, mask)
+            flops = 2 * pairs * nh * (dk + dv)
+            keys = batch * min(cached + q_len, mask.size or cached + q_len) if q_len == 1 else batch * (cached + q_len)
+            nbytes = 2 * (keys * nkv * (dk + (0 if vin else dv)) + 2 * batch * q_len * nh * (dk + dv) // 2)
+            out[f"{name}_{label}"] = dict(us=round(ms * 1e3, 1), tflops=round(flops / ms / 1e9, 1),
+                                          frac_bf16_peak_of_measured=round(flops / ms / 1e9 / pk["bf16_tflops"], 4),
+                                          gbs=round(nbytes / ms / 1e6, 1),
+                                          frac_hbm_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    # the closest model's kernels on its causal layer of the same head shape
+    nh, nkv, hd = s["heads"], s["kv_heads"], s["dim"]
+    for label, batch, cached, q_len in (("prefill_2048", 1, 0, T), ("decode_b8", 8, T - 1, 1), ("decode_b64", 64, T - 1, 1)):
+        if once:
+            continue
+        c, kc, vc, bt, npages = paged(batch, cached, q_len, nkv, hd, hd)
+        q = torch.randn(batch * q_len, nh, hd, device=DEV, dtype=torch.bfloat16)
+        o = torch.empty(batch * q_len, nh * hd, device=DEV, dtype=torch.bfloat16)
+        causal = ops.KeyMask.causal()
+        if q_len == 1:
+            ns = ops.decode_splits(batch, nkv, cached + 1, None)
+            po = torch.empty(batch, nh, ns, hd, device=DEV)
+            pml = torch.empty(batch, nh, ns, 2, device=DEV)
+            fn = lambda: ops.attention_decode_bf16(q, o, kc, vc, bt, c.positions, c.tok_seg, npages, None, hd ** -0.5, ns,
+                                                   po, pml, c.err)
+            variants = [("qwen2_causal", fn)]
+        else:
+            variants = [("qwen2_causal_tcgen05", lambda: ops.attention_prefill_tc(q, o, kc, vc, bt, c.seg_start, c.cached_len, q_len,
+                                                                                  npages, None, hd ** -0.5, c.err)),
+                        ("qwen2_causal_mma_sync", lambda: ops.attention_prefill_bf16(q, o, kc, vc, bt, c.seg_start, c.cached_len,
+                                                                                     q_len, npages, None, hd ** -0.5, c.err))]
+        for vname, fn in variants:
+            ms = timeit(fn)
+            pairs = batch * visible_pairs(cached, q_len, causal)
+            flops = 4 * pairs * nh * hd
+            nbytes = 2 * (batch * (cached + q_len) * nkv * 2 * hd + 2 * batch * q_len * nh * hd)
+            out[f"{vname}_{label}"] = dict(us=round(ms * 1e3, 1), tflops=round(flops / ms / 1e9, 1),
+                                           frac_bf16_peak_of_measured=round(flops / ms / 1e9 / pk["bf16_tflops"], 4),
+                                           gbs=round(nbytes / ms / 1e6, 1),
+                                           frac_hbm_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+    return out
+
+
+def run(sizes, steps, warmup, prompt_len=2048, batch=8, kernels_only=False, once=None, peaks=None):
+    pk = peaks or dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
+    result = dict(metric="prefill and decode tokens/s, Dolezen beside Qwen2 at equal size", unit="tokens/s", n_gpus=1,
+                  steps=steps, warmup=warmup, dtype="bf16", data="synthetic (random weights, random token ids)",
+                  peaks=pk, sizes={})
+    launches = 0
+    for name in sizes:
+        s = SIZES[name]
+        entry = dict(shape=s)
+        if not kernels_only and not once:
+            for label, raw in (("dolezen", dolezen_config(s)), ("qwen2", qwen2_config(s))):
+                entry[label] = engine_numbers(raw, prompt_len, batch, steps, warmup)
+                launches += entry[label].pop("launches")
+            entry["dolezen_over_qwen2"] = dict(
+                prefill=round(entry["dolezen"]["prefill_tokens_per_s"] / entry["qwen2"]["prefill_tokens_per_s"], 3),
+                decode=round(entry["dolezen"]["decode_tokens_per_s"] / entry["qwen2"]["decode_tokens_per_s"], 3))
+        entry["kernels"] = kernel_numbers(s, pk, once)
+        result["sizes"][name] = entry
+    result["gpu_launches"] = launches
+    result["config"] = dict(prompt_len=prompt_len, decode_batch=batch, page_size=PAGE, l2="inputs larger than L2 (weights); "
+                            "kernel timings flush L2 between launches")
+    return result
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sizes", default="2k,4k")
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--kernels-only", action="store_true")
+    ap.add_argument("--once", default=None, help="launch one kernel case a few times without timing (for a profiler)")
+    a = ap.parse_args(argv)
+    print(json.dumps(run(a.sizes.split(","), a.steps, max(3, a.warmup), kernels_only=a.kernels_only, once=a.once)))
+
+
+if __name__ == "__main__":
+    main()

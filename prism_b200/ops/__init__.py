@@ -337,10 +337,11 @@ def check_tc_errors():
             raise KernelError(f"tensor-core GEMM: device error {code} (a bounded wait ran out)")
 
 
-def linear_delta(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+def linear_delta(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, f32: bool = False) -> torch.Tensor:
     """A projection whose result will be added to the residual stream by the
     next norm: like ``linear``, but it may return a float32 stack ``[k, M, N]``
-    of partial sums over K, which the fused add + norm kernel adds up."""
+    of partial sums over K, which the fused add + norm kernel adds up.  ``f32``: the
+    result is float32 in any case (never rounded to 16 bits before the residual sum)."""
     if bias is None and tc_gemm_ok(x, w):
         N, K = w.shape
         ks = tc_ksplit(N, K, M=x.shape[0])
@@ -348,7 +349,7 @@ def linear_delta(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
             out = torch.empty((ks, x.shape[0], N), dtype=torch.float32, device=x.device)
             gemm_tc(x, w, None, out, EPI_PARTIAL, ksplit=ks)
             return out
-    return linear(x, w, bias)
+    return linear(x, w, bias, out_dtype=torch.float32 if f32 else None)
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
@@ -1322,13 +1323,20 @@ def attention_masked_bf16(q, out, k_plane, v_plane, block_table, seg_start, cach
         1 if few_rows else 0, _ptr(err), _stream()), "attention_masked_bf16")
 
 
-def feed_forward_act(ctx, x: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, kind: str,
-                     up_b: Optional[torch.Tensor] = None, down_b: Optional[torch.Tensor] = None):
+def feed_forward_hidden(ctx, x: torch.Tensor, up_w: Optional[torch.Tensor], kind: str, out: torch.Tensor,
+                        hidden: Optional[torch.Tensor] = None):
+    """``out = act(up(x))``; ``hidden``: the up projection if another product has made it already.  ``out``
+    may be a column block of a wider buffer."""
+    if hidden is None:
+        hidden = linear(x, up_w)
+    activation(hidden, out, kind)
+
+
+def feed_forward_act(ctx, x: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, kind: str):
     """``down(act(up(x)))``."""
-    hidden = linear(x, up_w, up_b)
-    act = ctx.alloc(hidden.shape, x.dtype)
-    activation(hidden, act, kind)
-    return linear_delta(act, down_w, down_b)
+    act = ctx.alloc((x.shape[0], up_w.shape[0]), x.dtype)
+    feed_forward_hidden(ctx, x, up_w, kind, act)
+    return linear_delta(act, down_w)
 
 
 def stack_deltas(ctx, deltas):

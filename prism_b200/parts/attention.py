@@ -17,7 +17,7 @@ from typing import Optional
 import torch
 
 from ..config.model_config import ConfigError
-from .base import CacheNeed, Mixer, ParamSpec, PartSpec, WeightSource, build_part, register_part
+from .base import CacheNeed, DetachedProjection, Mixer, ParamSpec, PartSpec, WeightSource, build_part, register_part
 from .. import ops
 
 
@@ -66,6 +66,7 @@ class GQAAttention(Mixer):
         # what the fused rotate-and-store and the equal-size attention kernels do not cover goes the general way:
         # projection, (rotation,) one store per plane, attention under a KeyMask
         self.general = self.vhd != self.hd or self.chunk is not None or self.sink or not self.own_kv
+        self._own_in = self._own_out = True
         self.mask = ops.KeyMask.chunk(self.chunk) if self.chunk is not None else ops.KeyMask.window(self.window)
 
     @property
@@ -84,22 +85,58 @@ class GQAAttention(Mixer):
         return CacheNeed("paged", self.nkv, self.hd, self.window,
                          v_head_dim=None if self.vhd == self.hd else self.vhd, chunk=self.cache_chunk)
 
-    def params(self):
+    def _in_sources(self):
         H, qs, kvs, vs, n = self.hidden_size, self.q_size, self.kv_size, self.v_size, self.names
         w = [WeightSource(n["q"], (qs, H))]
         b = [WeightSource(n["q_b"], (qs,), "bias")]
         if self.own_kv:
             w += [WeightSource(n["k"], (kvs, H)), WeightSource(n["v"], (vs, H))]
             b += [WeightSource(n["k_b"], (kvs,), "bias"), WeightSource(n["v_b"], (vs,), "bias")]
-        ps = [ParamSpec("qkv_w", tuple(w))]
-        if self.qkv_bias:
-            ps.append(ParamSpec("qkv_b", tuple(b)))
+        return tuple(w), tuple(b) if self.qkv_bias else ()
+
+    def _out_sources(self):
+        n = self.names
+        return ((WeightSource(n["o"], (self.hidden_size, self.nh * self.vhd)),),
+                (WeightSource(n["o_b"], (self.hidden_size,), "bias"),) if self.o_bias else ())
+
+    def params(self):
+        ps = []
+        if self._own_in:
+            w, b = self._in_sources()
+            ps.append(ParamSpec("qkv_w", w))
+            if b:
+                ps.append(ParamSpec("qkv_b", b))
         if self.sink:
-            ps.append(ParamSpec("sink", (WeightSource(n["sink"], (self.nh,), "bias"),)))
-        ps.append(ParamSpec("o_w", (WeightSource(n["o"], (H, self.nh * self.vhd)),)))
-        if self.o_bias:
-            ps.append(ParamSpec("o_b", (WeightSource(n["o_b"], (H,), "bias"),)))
+            ps.append(ParamSpec("sink", (WeightSource(self.names["sink"], (self.nh,), "bias"),)))
+        if self._own_out:
+            w, b = self._out_sources()
+            ps.append(ParamSpec("o_w", w))
+            if b:
+                ps.append(ParamSpec("o_b", b))
         return ps
+
+    # only the general path hands its projections to the block: the other one has fused kernels of its own
+    @property
+    def detachable_out(self):
+        return self.general
+
+    @property
+    def detachable_in(self):
+        return self.general
+
+    def detach_out_projection(self):
+        if not self.general:
+            return None
+        self._own_out = False
+        w, b = self._out_sources()
+        return DetachedProjection(self.handed_over(*w), self.handed_over(*b), self.nh * self.vhd)
+
+    def detach_in_projection(self):
+        if not self.general:
+            return None
+        self._own_in = False
+        w, b = self._in_sources()
+        return DetachedProjection(self.handed_over(*w), self.handed_over(*b), sum(s.shape[0] for s in w))
 
     def on_bound(self):
         # Said once, when the model is built, not found out from the step time: in bfloat16 the tensor-core
@@ -116,14 +153,14 @@ class GQAAttention(Mixer):
                               f"and up to 16 query heads per kv head): correct, but much slower", RuntimeWarning,
                               stacklevel=2)
 
-    def _forward_general(self, ctx, x, cache):
-        """Projection (+ bias), rotation if the layer has one, one store per cache plane, attention under the
-        layer's mask with its sink, output projection."""
+    def forward_inner(self, ctx, x, cache, out, proj=None):
+        """Projection (+ bias; ``proj``: made by the block already), rotation if the layer has one, one store
+        per cache plane, attention under the layer's mask with its sink into ``out [T, nh * vhd]``."""
         T, qs, kvs = x.shape[0], self.q_size, self.kv_size
         if cache.write != self.own_kv:
             raise ValueError("a layer without key and value projections must read another run's cache plane, "
                              "and one with them owns its plane")
-        qkv = ops.linear(x, self.w["qkv_w"], self.w.get("qkv_b"))
+        qkv = proj if proj is not None else ops.linear(x, self.w["qkv_w"], self.w.get("qkv_b"))
         q = qkv[:, :qs].view(T, self.nh, self.hd)
         k = qkv[:, qs:qs + kvs].view(T, self.nkv, self.hd) if self.own_kv else None
         if self.position is not None:
@@ -139,14 +176,14 @@ class GQAAttention(Mixer):
                             ctx.max_positions, ctx.err)
             ops.cache_store(qkv[:, qs + kvs:], cache.v, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages,
                             ctx.max_positions, ctx.err)
-        attn = ctx.alloc((T, self.nh * self.vhd), x.dtype)
-        ops.masked_attention(ctx, q, attn, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
+        ops.masked_attention(ctx, q, out, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
                              self.w.get("sink"))
-        return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))
 
     def forward(self, ctx, x, cache):
         if self.general:
-            return self._forward_general(ctx, x, cache)
+            attn = ctx.alloc((x.shape[0], self.nh * self.vhd), x.dtype)
+            self.forward_inner(ctx, x, cache, attn)
+            return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))
         T, qs, kvs = x.shape[0], self.q_size, self.kv_size
         rot = self.position.rotary() if self.position is not None else None
         if rot is None and self.position is not None:
@@ -211,6 +248,7 @@ class LatentAttention(Mixer):
         self.scale = float(scale) if scale is not None else (self.hd + self.rd) ** -0.5
         self.names = dict(self.NAMES, **(names or {}))
         self.mask = ops.KeyMask.window(self.window)
+        self._own_out = True
 
     def cache_need(self):
         return CacheNeed("paged", 1, self.kv_rank + self.rd, self.window, v_head_dim=0)
@@ -225,8 +263,16 @@ class LatentAttention(Mixer):
             ParamSpec("uq_w", (WeightSource(n["uq"], (nh * (self.hd + self.rd), self.q_rank)),)),
             ParamSpec("uk_w", (WeightSource(n["uk"], (nh * self.hd, self.kv_rank)),)),
             ParamSpec("uv_w", (WeightSource(n["uv"], (nh * self.vhd, self.kv_rank)),)),
-            ParamSpec("o_w", (WeightSource(n["o"], (H, nh * self.vhd)),)),
-        ]
+        ] + ([ParamSpec("o_w", (self._o_source(),))] if self._own_out else [])
+
+    detachable_out = True        # the down projections feed norms and stay float32: they are not handed over
+
+    def _o_source(self):
+        return WeightSource(self.names["o"], (self.hidden_size, self.nh * self.vhd))
+
+    def detach_out_projection(self):
+        self._own_out = False
+        return DetachedProjection(self.handed_over(self._o_source()), (), self.nh * self.vhd)
 
     def on_bound(self):
         half = self.rope_dims // 2
@@ -237,6 +283,11 @@ class LatentAttention(Mixer):
         self.uv = self.w["uv_w"].view(self.nh, self.vhd, self.kv_rank)                                  # [nh, vhd, R]
 
     def forward(self, ctx, x, cache):
+        attn = ctx.alloc((x.shape[0], self.nh * self.vhd), x.dtype)
+        self.forward_inner(ctx, x, cache, attn)
+        return ops.linear_delta(attn, self.w["o_w"])
+
+    def forward_inner(self, ctx, x, cache, out, proj=None):
         T, nh, hd, rd, R = x.shape[0], self.nh, self.hd, self.rd, self.kv_rank
         # both down projections in one product; float32, because each feeds a norm
         down = ops.linear(x, self.w["down_w"], None, out_dtype=torch.float32)
@@ -253,6 +304,4 @@ class LatentAttention(Mixer):
         lat = ctx.alloc((T, nh * R), x.dtype)
         ops.masked_attention(ctx, qf, lat, cache.k, cache.k[..., :R], cache.block_table, cache.num_pages, self.mask,
                              self.scale, None)
-        attn = ctx.alloc((T, nh * self.vhd), x.dtype)
-        ops.matmul_heads(lat.view(T, nh, R), self.uv, attn.view(T, nh, self.vhd))
-        return ops.linear_delta(attn, self.w["o_w"])
+        ops.matmul_heads(lat.view(T, nh, R), self.uv, out.view(T, nh, self.vhd))

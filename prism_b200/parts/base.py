@@ -35,17 +35,21 @@ from typing import Callable, Dict, List, Optional, Tuple
 class WeightSource:
     """One tensor of the model file: its name relative to the part's prefix,
     its shape, and how random-weights mode draws it
-    (``matrix`` | ``bias`` | ``norm``)."""
+    (``matrix`` | ``bias`` | ``norm``).  ``absolute``: the name is the file's
+    full name already (a tensor that another part has handed over)."""
     name: str
     shape: Tuple[int, ...]
     init: str = "matrix"
+    absolute: bool = False
 
 
 @dataclass(frozen=True)
 class ParamSpec:
     """One parameter of a part as the kernels see it: the file tensors in
     ``sources`` stacked along dim 0 (the fused qkv and gate_up buffers of
-    engine/weight_pool.py:169-182,194-197).  ``optional``: all sources may be
+    engine/weight_pool.py:169-182,194-197), or with ``axis=1`` side by side
+    along dim 1 (projections whose results are added: one product over the
+    joined inputs).  ``optional``: all sources may be
     absent together, and then ``absent`` says what the part gets: ``"zeros"``
     or ``"none"``.  ``alias_of`` names another parameter (qualified) whose
     storage is shared when every source is absent (a tied head)."""
@@ -54,10 +58,13 @@ class ParamSpec:
     optional: bool = False
     absent: str = "none"
     alias_of: Optional[str] = None
+    axis: int = 0
 
     @property
     def shape(self) -> Tuple[int, ...]:
         first = self.sources[0].shape
+        if self.axis == 1:
+            return (first[0], sum(s.shape[1] for s in self.sources)) + tuple(first[2:])
         return (sum(s.shape[0] for s in self.sources),) + tuple(first[1:])
 
 
@@ -111,6 +118,16 @@ class RotaryParams:
     rotary_dim: int
 
 
+@dataclass(frozen=True)
+class DetachedProjection:
+    """A projection that a part hands to the block around it: its weight's file tensors (names relative to
+    the block's prefix; several are stacked along dim 0), their biases if any, and its width - the columns
+    it reads (an output projection) or the rows it produces (an input projection)."""
+    weights: Tuple[WeightSource, ...]
+    biases: Tuple[WeightSource, ...]
+    width: int
+
+
 # --------------------------------------------------------------------------
 # part base classes
 # --------------------------------------------------------------------------
@@ -151,8 +168,9 @@ class Part:
         """Yield ``(qualified name, ParamSpec with absolute tensor names)`` for
         this part and everything below it."""
         for p in self.params():
-            srcs = tuple(WeightSource(self.prefix + s.name, s.shape, s.init) for s in p.sources)
-            yield path + p.name, ParamSpec(p.name, srcs, p.optional, p.absent, p.alias_of)
+            srcs = tuple(WeightSource(s.name if s.absolute else self.prefix + s.name, s.shape, s.init, True)
+                         for s in p.sources)
+            yield path + p.name, ParamSpec(p.name, srcs, p.optional, p.absent, p.alias_of, p.axis)
         for cname, child in self.children.items():
             yield from child.named_params(f"{path}{cname}.")
 
@@ -167,6 +185,10 @@ class Part:
 
     def on_bound(self) -> None:
         """Hook: create device buffers that are not weights (tables, scratch)."""
+
+    def handed_over(self, *sources: WeightSource) -> Tuple[WeightSource, ...]:
+        """Own file tensors under their full names, for a ``DetachedProjection``."""
+        return tuple(WeightSource(s.name if s.absolute else self.prefix + s.name, s.shape, s.init, True) for s in sources)
 
     def walk(self):
         """This part and every part below it."""
@@ -200,6 +222,8 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     category = "mixer"
+    detachable_out = False      # whether detach_out_projection / detach_in_projection hand anything over
+    detachable_in = False
     # Whether a pure-decode step with this mixer may be replayed from a captured CUDA graph.  Inside a
     # graph there is no host copy of the step (``ctx.host`` and ``StateCacheView.host_slots`` are None)
     # and every value must come from device arrays.  None: yes unless the mixer keeps per-request state
@@ -216,11 +240,40 @@ class Mixer(Part):
         mixer needs none)."""
         raise NotImplementedError
 
+    # A block that adds the results of several sublayers may take over their last projections and run them
+    # as one product over the joined inputs (see ``parts/blocks.py``), and likewise their first projections
+    # of the same input.  A part that can hand them over implements these; the default is that it cannot.
+    def detach_out_projection(self) -> Optional["DetachedProjection"]:
+        """Give up the output projection: from now on ``params()`` leaves it out and ``forward_inner`` is
+        called instead of ``forward``.  None: this part keeps it."""
+        return None
+
+    def detach_in_projection(self) -> Optional["DetachedProjection"]:
+        """Give up the first projection of the layer's input (only after ``detach_out_projection``):
+        ``forward_inner`` then gets its columns of the joint product as ``proj``."""
+        return None
+
+    def forward_inner(self, ctx, x, cache, out, proj=None) -> None:
+        """The sublayer up to its output projection, written into ``out [T, inner]`` (a view whose rows may
+        have a stride of their own)."""
+        raise NotImplementedError
+
 
 class FeedForward(Part):
     category = "feed_forward"
+    detachable_out = False
+    detachable_in = False
 
     def forward(self, ctx, x):
+        raise NotImplementedError
+
+    def detach_out_projection(self) -> Optional["DetachedProjection"]:
+        return None
+
+    def detach_in_projection(self) -> Optional["DetachedProjection"]:
+        return None
+
+    def forward_inner(self, ctx, x, out, proj=None) -> None:
         raise NotImplementedError
 
 

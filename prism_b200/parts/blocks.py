@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from typing import Optional
 
-from .base import Block, PartSpec, build_part, register_part
+from .base import Block, ParamSpec, PartSpec, build_part, register_part
 from .. import ops
 
 
@@ -31,20 +31,68 @@ class PreNormBlock(Block):
 
 @register_part("block", "parallel")
 class ParallelBlock(Block):
-    """``h = norm(x); x += mixer(h) + feed_forward(h)``.  The two results travel to the next norm as a
-    float32 stack ``[2, T, H]`` and are added to the float32 residual there, so the sum is never rounded
-    to 16 bits.  ``feed_forward`` None: the layer has a mixer only."""
+    """``h = norm(x); x += mixer(h) + feed_forward(h)``.
 
-    def __init__(self, mixer: PartSpec, norm: PartSpec, feed_forward: Optional[PartSpec] = None):
+    Where both sublayers can hand over their output projections (``detach_out_projection``), the block runs
+    them as one product: ``[mixer's inner output | feed-forward's hidden layer] @ [W_o | W_down]^T (+ bias)``,
+    so the two results are added inside the product's float32 accumulator and reach the residual stream as
+    one float32 delta.  Where both can also hand over their first projections of h, those are one product as
+    well (q, k, v and the feed-forward's up projection read the same h).  Otherwise the two results travel to
+    the next norm as a float32 stack ``[2, T, H]`` and are added to the float32 residual there; either way
+    the sum is never rounded to 16 bits.  ``feed_forward`` None: the layer has a mixer only.  ``fuse``
+    False keeps every projection with its part."""
+
+    def __init__(self, mixer: PartSpec, norm: PartSpec, feed_forward: Optional[PartSpec] = None, fuse: bool = True):
         self.norm = self.add_child("norm", build_part("norm", norm))
         self.mixer = self.add_child("mixer", build_part("mixer", mixer))
         self.feed_forward = (self.add_child("feed_forward", build_part("feed_forward", feed_forward))
                              if feed_forward is not None else None)
+        self.out_m = self.out_f = self.in_m = self.in_f = None
+        ff = self.feed_forward
+        if fuse and ff is not None and self.mixer.detachable_out and ff.detachable_out:
+            self.out_m, self.out_f = self.mixer.detach_out_projection(), ff.detach_out_projection()
+            if self.out_m.biases and self.out_f.biases:
+                raise ValueError("parallel block: at most one of the two output projections may have a bias")
+            if self.mixer.detachable_in and ff.detachable_in:
+                self.in_m, self.in_f = self.mixer.detach_in_projection(), ff.detach_in_projection()
+
+    def params(self):
+        ps = []
+        if self.in_m is not None:
+            ps.append(ParamSpec("in_w", self.in_m.weights + self.in_f.weights))
+            for name, d in (("in_b_mixer", self.in_m), ("in_b_ff", self.in_f)):
+                if d.biases:
+                    ps.append(ParamSpec(name, d.biases))
+        if self.out_m is not None:
+            ps.append(ParamSpec("out_w", self.out_m.weights + self.out_f.weights, axis=1))
+            if self.out_m.biases or self.out_f.biases:
+                ps.append(ParamSpec("out_b", self.out_m.biases or self.out_f.biases))
+        return ps
+
+    def on_bound(self):
+        self.in_b = None
+        if self.in_m is not None and (self.in_m.biases or self.in_f.biases):
+            # one bias vector for the joint product: zeros for the rows of the part that has none
+            bm, bf = self.w.get("in_b_mixer"), self.w.get("in_b_ff")
+            ref = bm if bm is not None else bf
+            zeros = lambda n: ops.torch.zeros(n, dtype=ref.dtype, device=ref.device)
+            self.in_b = ops.torch.cat([bm if bm is not None else zeros(self.in_m.width),
+                                       bf if bf is not None else zeros(self.in_f.width)])
 
     def forward(self, ctx, residual, delta, cache):
         h = self.norm.forward(ctx, residual, delta)
-        d_mix = self.mixer.forward(ctx, h, cache)
         if self.feed_forward is None:
-            return residual, d_mix
-        d_ff = self.feed_forward.forward(ctx, h)
-        return residual, ops.stack_deltas(ctx, (d_mix, d_ff))
+            return residual, self.mixer.forward(ctx, h, cache)
+        if self.out_m is None:
+            d_mix = self.mixer.forward(ctx, h, cache)
+            d_ff = self.feed_forward.forward(ctx, h)
+            return residual, ops.stack_deltas(ctx, (d_mix, d_ff))
+        wm = self.out_m.width
+        inner = ctx.alloc((h.shape[0], wm + self.out_f.width), h.dtype)
+        pm = pf = None
+        if self.in_m is not None:
+            proj = ops.linear(h, self.w["in_w"], self.in_b)
+            pm, pf = proj[:, :self.in_m.width], proj[:, self.in_m.width:]
+        self.mixer.forward_inner(ctx, h, cache, inner[:, :wm], pm)
+        self.feed_forward.forward_inner(ctx, h, inner[:, wm:], pf)
+        return residual, ops.linear_delta(inner, self.w["out_w"], self.w.get("out_b"), f32=True)

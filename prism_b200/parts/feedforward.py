@@ -5,7 +5,7 @@ projection, an elementwise activation, down projection."""
 
 from __future__ import annotations
 
-from .base import FeedForward, ParamSpec, WeightSource, register_part
+from .base import DetachedProjection, FeedForward, ParamSpec, WeightSource, register_part
 from .. import ops
 
 
@@ -40,11 +40,28 @@ class ActMLP(FeedForward):
         self.intermediate_size = int(intermediate_size)
         self.activation = activation
         self.names = tuple(names)
+        self._own_up = self._own_down = True
+
+    detachable_out = detachable_in = True
+
+    def _sources(self):
+        H, I = self.hidden_size, self.intermediate_size
+        return WeightSource(self.names[0], (I, H)), WeightSource(self.names[1], (H, I))
 
     def params(self):
-        H, I = self.hidden_size, self.intermediate_size
-        return [ParamSpec("up_w", (WeightSource(self.names[0], (I, H)),)),
-                ParamSpec("down_w", (WeightSource(self.names[1], (H, I)),))]
+        up, down = self._sources()
+        return ([ParamSpec("up_w", (up,))] if self._own_up else []) + ([ParamSpec("down_w", (down,))] if self._own_down else [])
+
+    def detach_out_projection(self):
+        self._own_down = False
+        return DetachedProjection(self.handed_over(self._sources()[1]), (), self.intermediate_size)
+
+    def detach_in_projection(self):
+        self._own_up = False
+        return DetachedProjection(self.handed_over(self._sources()[0]), (), self.intermediate_size)
+
+    def forward_inner(self, ctx, x, out, proj=None):
+        ops.feed_forward_hidden(ctx, x, self.w.get("up_w"), self.activation, out, hidden=proj)
 
     def forward(self, ctx, x):
         return ops.feed_forward_act(ctx, x, self.w["up_w"], self.w["down_w"], self.activation)

@@ -61,7 +61,8 @@ class StaticWeightPool:
         return self.tensors[name]
 
     def source_view(self, qname: str, source_index: int) -> torch.Tensor:
-        """The rows of a fused parameter that one file tensor fills."""
+        """The rows (columns, for a parameter stacked along dim 1) of a fused parameter that one file tensor fills."""
         spec = self.specs[qname]
-        start = sum(s.shape[0] for s in spec.sources[:source_index])
-        return self.tensors[qname][start:start + spec.sources[source_index].shape[0]]
+        ax = spec.axis
+        start = sum(s.shape[ax] for s in spec.sources[:source_index])
+        return self.tensors[qname].narrow(ax, start, spec.sources[source_index].shape[ax])

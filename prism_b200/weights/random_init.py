@@ -81,7 +81,10 @@ def random_pool(model, seed: int, device, compute_dtype: torch.dtype) -> StaticW
         for i, s in enumerate(spec.sources):
             gen = torch.Generator(device=device).manual_seed(int(seed) + idx)
             view = pool.source_view(q, i)
-            view.normal_(0.0, STD, generator=gen)
+            if view.is_contiguous():
+                view.normal_(0.0, STD, generator=gen)
+            else:       # columns of a parameter stacked along dim 1: drawn as the file's tensor is, then placed
+                view.copy_(torch.empty(view.shape, dtype=view.dtype, device=view.device).normal_(0.0, STD, generator=gen))
             if s.init == "norm":
                 view.add_(1.0)
             idx += 1

@@ -59,6 +59,15 @@ def chunk_mask(T, size):
     return (j <= i) & (i // size == j // size)
 
 
+def layer_mask(T, mx, kind):
+    """The mask of a mixer: ``kind`` ('sliding' or 'chunk') with the size the configuration gives; a mixer
+    without a mask sees every earlier key."""
+    size = (mx.get("mask") or {}).get("size")
+    if size is None:
+        return chunk_mask(T, max(T, 1))
+    return sliding_mask(T, size) if kind == "sliding" else chunk_mask(T, size)
+
+
 # ---- softmax ----------------------------------------------------------------------
 
 def masked_softmax(scores, mask, sink=None):
@@ -97,7 +106,7 @@ def sink_attention(h, w, pre, mx, kv):
     kk = k.repeat_interleave(rep, dim=1)                      # query head a uses kv head a // rep
     vv = v.repeat_interleave(rep, dim=1)
     scores = torch.einsum("iad,jad->aij", q, kk) * mx["scale"]
-    p = masked_softmax(scores, chunk_mask(T, mx["mask"]["size"]), w[pre + "sink"])
+    p = masked_softmax(scores, layer_mask(T, mx, "chunk"), w[pre + "sink"])
     o = torch.einsum("aij,jad->iad", p, vv).reshape(T, H * dv)
     return o @ w[pre + "o"].T + w[pre + "o.b"]
 
@@ -118,7 +127,7 @@ def latent_attention(h, w, pre, mx, eps):
     v = (c @ w[pre + "uv"].T).view(T, H, dv)
     scores = (torch.einsum("iad,jad->aij", q_plain, k_plain) +
               torch.einsum("iad,jd->aij", q_rot, k_rot)) * mx["scale"]
-    p = masked_softmax(scores, sliding_mask(T, mx["mask"]["size"]))
+    p = masked_softmax(scores, layer_mask(T, mx, "sliding"))
     o = torch.einsum("aij,jad->iad", p, v).reshape(T, H * dv)
     return o @ w[pre + "o"].T
 

@@ -206,14 +206,16 @@ def test_latent_cache_row_and_query_rotation(dtype, R, r, dims):
     for t, p in enumerate(pos):
         row = plane[bt[0, p // page].item(), p % page, 0].float().cpu()
         assert torch.allclose(row[:R], c[t], atol=tol * 4), (t, (row[:R] - c[t]).abs().max())
-        assert torch.allclose(row[R:], kr[t], atol=tol * 60), (t, (row[R:] - kr[t]).abs().max())
+        # the kernel forms the angle position * frequency in float32, the plain code in float64: at position p the
+        # two differ by up to p * 2^-24 radians, times entries of up to about 10
+        assert torch.allclose(row[R:], kr[t], atol=tol * 60 + p * 1.2e-6), (t, (row[R:] - kr[t]).abs().max())
     assert int((plane[7] != 0).sum()) == 0 and int((plane[3:5] != 0).sum()) == 0
     if r:
         src = (torch.randn(T, 3, 7 + r, generator=g)).to(dtype).to(DEV)
         dst = torch.zeros(T, 3, 11 + r, dtype=dtype, device=DEV)
         ops.rotate_slice(src[:, :, 7:], dst[:, :, 11:], dims, inv, i32(pos))
         ref = DP.rotate(src[:, :, 7:].float().cpu(), torch.tensor(pos), 50.0, dims)
-        assert torch.allclose(dst[:, :, 11:].float().cpu(), ref, atol=3e-4 if dtype == torch.float32 else 3e-2)
+        assert torch.allclose(dst[:, :, 11:].float().cpu(), ref, atol=4e-3 if dtype == torch.float32 else 3e-2)
         assert float(dst[:, :, :11].abs().max()) == 0
 
 
