@@ -146,6 +146,7 @@ def paged(batch, ctx, q_len, nkv, dk, dv, values_in_keys=False):
         positions=i32(torch.cat([torch.arange(ctx, ctx + q_len) for _ in range(batch)])),
         tok_seg=i32(torch.arange(batch).repeat_interleave(q_len)), seg_start=i32(torch.arange(batch + 1) * q_len),
         cached_len=torch.full((batch,), ctx, dtype=torch.int32, device=DEV), S=batch, max_q_len=q_len,
+        max_kv_len=ctx + q_len,
         decode_only=q_len == 1, err=torch.zeros(1, dtype=torch.int32, device=DEV))
     return ctx_ns, kc, vc, bt, n_pages
 

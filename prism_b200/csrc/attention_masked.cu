@@ -53,6 +53,10 @@ struct MaskedAttn {
     int rpt;           // rows per token: the query heads of one kv head (at most 64 of them per CTA)
     int tok_per_cta;   // 64 / rpt
     int hgroups;       // CTAs that share the heads of one kv head when there are more than 64
+    int page_shift;    // log2(page_size), or -1
+    int nsplit;        // few-rows shape: CTAs that share one (segment, kv head)'s key tiles
+    float* part_o;     // [segments, nh, nsplit, dv]   their partial outputs (not normalised) ...
+    float* part_ml;    // [segments, nh, nsplit, 2]    ... with running maximum (log2 domain) and sum
 };
 
 __device__ __forceinline__ int ma_first_key(int kind, int size, int pos) {
@@ -67,28 +71,47 @@ __device__ __forceinline__ float ma_exp2(float x) {      // 0 for -inf
     return y;
 }
 
-// 64 cache rows (keys first_key ..) of one kv head into dst[64][stride]: `chunks` 16-byte pieces a row, of
-// which the first `real` come from the plane and the rest are zero; keys outside [lo, hi] are zero rows.
-__device__ __forceinline__ void ma_load_rows(__nv_bfloat16* dst, int stride, int chunks, int real,
-                                             const __nv_bfloat16* __restrict__ plane, long long row_stride,
-                                             size_t head_off, const int* __restrict__ bt, int first_key, int lo, int hi,
-                                             int page_size, int num_pages, int* err, int tid) {
-    const int items = MA_TILE * chunks;
-    for (int i = tid; i < items; i += MA_THREADS) {
-        const int r = i / chunks, c = i - r * chunks;
-        const int key = first_key + r;
-        bool valid = key >= lo && key <= hi && c < real;
-        size_t off = 0;
-        if (valid) {
-            const int page = bt[key / page_size];
-            if (page < 0 || page >= num_pages) {
-                report_error(err, PRISM_ERR_PAGE_RANGE);
-                valid = false;
-            } else {
-                off = ((size_t)page * page_size + key % page_size) * (size_t)row_stride + head_off + (size_t)c * 8;
+// 64 cache rows (keys first_key ..) of one kv head into ks[64][kstride] and, unless the values are read out of
+// the key rows, vs[64][vstride].  A row is `kchunks` (`vchunks`) 16-byte pieces, of which the first `kreal`
+// (`vreal`) come from the plane and the rest are zero; keys outside [lo, hi] are zero rows.  Sixteen threads
+// share a row and a thread serves rows tid / 16 + 8 j: it first looks up the slots of its eight rows (eight
+// independent loads of the block table, in flight together), then issues the copies.
+template <bool WITH_V>
+__device__ __forceinline__ void ma_load_tile(__nv_bfloat16* ks, int kstride, int kchunks, int kreal,
+                                             __nv_bfloat16* vs, int vstride, int vchunks, int vreal,
+                                             const __nv_bfloat16* __restrict__ kplane, long long k_row_stride, size_t k_head_off,
+                                             const __nv_bfloat16* __restrict__ vplane, long long v_row_stride, size_t v_head_off,
+                                             const int* __restrict__ bt, int first_key, int lo, int hi,
+                                             int page_size, int page_shift, int num_pages, int* err, int tid) {
+    const int rr = tid >> 4, cc = tid & 15;
+    long long slot[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int key = first_key + rr + 8 * j;
+        slot[j] = -1;
+        if (key >= lo && key <= hi) {
+            const int page = page_shift >= 0 ? bt[key >> page_shift] : bt[key / page_size];
+            const int in_page = page_shift >= 0 ? (key & (page_size - 1)) : key % page_size;
+            if (page < 0 || page >= num_pages) report_error(err, PRISM_ERR_PAGE_RANGE);
+            else slot[j] = (long long)page * page_size + in_page;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int r = rr + 8 * j;
+        const bool row_ok = slot[j] >= 0;
+        const __nv_bfloat16* ksrc = kplane + (row_ok ? (size_t)slot[j] * (size_t)k_row_stride + k_head_off : 0);
+        for (int c = cc; c < kchunks; c += 16) {
+            const bool v = row_ok && c < kreal;
+            cp_async16(ks + r * kstride + c * 8, v ? ksrc + c * 8 : kplane, v);
+        }
+        if (WITH_V) {
+            const __nv_bfloat16* vsrc = vplane + (row_ok ? (size_t)slot[j] * (size_t)v_row_stride + v_head_off : 0);
+            for (int c = cc; c < vchunks; c += 16) {
+                const bool v = row_ok && c < vreal;
+                cp_async16(vs + r * vstride + c * 8, v ? vsrc + c * 8 : vplane, v);
             }
         }
-        cp_async16(dst + r * stride + c * 8, plane + off, valid);
     }
 }
 
@@ -98,10 +121,13 @@ attn_masked_kernel(const MaskedAttn a) {
     pdl_trigger();
     pdl_wait();
     constexpr int NT = SPLITK ? 2 : 8;                 // 8-key score tiles per warp and key tile
+    constexpr int STAGES = SPLITK ? 3 : 2;             // a decode CTA has little to compute: more tiles in flight
+    constexpr int QROWS = SPLITK ? 16 : MA_ROWS;       // query rows the CTA keeps in shared memory
     const int seg = blockIdx.z;
     const int kvh = blockIdx.y / a.hgroups, hg = blockIdx.y % a.hgroups;
     const int s0 = a.seg_start[seg], qlen = a.seg_start[seg + 1] - s0;
-    const int q0 = (gridDim.x - 1 - blockIdx.x) * a.tok_per_cta;          // later tiles see more keys: first
+    // later row tiles see more keys: they start first.  In the few-rows shape x counts the key splits instead.
+    const int q0 = SPLITK ? 0 : (gridDim.x - 1 - blockIdx.x) * a.tok_per_cta;
     if (q0 >= qlen) return;
     const int ntok = min(a.tok_per_cta, qlen - q0);
     const int rep = a.nh / a.nkv;
@@ -113,17 +139,22 @@ attn_masked_kernel(const MaskedAttn a) {
     const int kstride = a.dkp + 8, vstride = V_IN_K ? kstride : DVP + 8;
     const int k_elems = MA_TILE * kstride, v_elems = V_IN_K ? 0 : MA_TILE * vstride;
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [64][kstride]
-    __nv_bfloat16* KV = Qs + MA_ROWS * kstride;                                 // [stage][K | V]
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [QROWS][kstride]
+    __nv_bfloat16* KV = Qs + QROWS * kstride;                                   // [stage][K | V]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lo = ma_first_key(a.mask_kind, a.mask_size, pos0);
     const int hi = pos0 + ntok - 1;
-    const int t0 = lo / MA_TILE, t1 = hi / MA_TILE + 1;
+    int t0 = lo / MA_TILE, t1 = hi / MA_TILE + 1;
+    if (SPLITK && a.nsplit > 1) {                      // this CTA's share of the key tiles (it may be empty)
+        const int per = (t1 - t0 + a.nsplit - 1) / a.nsplit;
+        t0 += blockIdx.x * per;
+        t1 = min(t1, t0 + per);
+    }
 
     {   // the CTA's query rows
         const int chunks = a.dkp / 8, real = a.dk / 8;
-        for (int i = tid; i < MA_ROWS * chunks; i += MA_THREADS) {
+        for (int i = tid; i < QROWS * chunks; i += MA_THREADS) {
             const int r = i / chunks, c = i - r * chunks;
             const int tk = r / a.rpt, hh = r - tk * a.rpt;
             const bool valid = tk < ntok && hh < nheads && c < real;
@@ -134,14 +165,16 @@ attn_masked_kernel(const MaskedAttn a) {
     }
     auto load_tile = [&](int tile, int stage) {
         __nv_bfloat16* ks = KV + (size_t)stage * (k_elems + v_elems);
-        ma_load_rows(ks, kstride, a.dkp / 8, a.dk / 8, a.kc, a.k_row_stride, (size_t)kvh * a.k_head_stride, bt,
-                     tile * MA_TILE, lo, hi, a.page_size, a.num_pages, a.err, tid);
-        if (!V_IN_K)
-            ma_load_rows(ks + k_elems, vstride, DVP / 8, (a.dv + 7) / 8, a.vc, a.v_row_stride,
-                         (size_t)kvh * a.v_head_stride, bt, tile * MA_TILE, lo, hi, a.page_size, a.num_pages, a.err, tid);
+        ma_load_tile<!V_IN_K>(ks, kstride, a.dkp / 8, a.dk / 8, ks + k_elems, vstride, DVP / 8, (a.dv + 7) / 8, a.kc,
+                              a.k_row_stride, (size_t)kvh * a.k_head_stride, a.vc, a.v_row_stride,
+                              (size_t)kvh * a.v_head_stride, bt, tile * MA_TILE, lo, hi, a.page_size, a.page_shift,
+                              a.num_pages, a.err, tid);
     };
-    load_tile(t0, 0);
-    cp_async_commit();
+#pragma unroll
+    for (int st = 0; st < STAGES - 1; ++st) {           // the first group also holds the query rows
+        if (t0 + st < t1) load_tile(t0 + st, st);
+        cp_async_commit();
+    }
 
     float o[DVP / 8][4];
 #pragma unroll
@@ -165,14 +198,16 @@ attn_masked_kernel(const MaskedAttn a) {
     const int w_tk0 = min(rowbase / a.rpt, ntok - 1), w_tk1 = min((rowbase + 15) / a.rpt, ntok - 1);
     const int w_lo = ma_first_key(a.mask_kind, a.mask_size, pos0 + w_tk0), w_hi = pos0 + w_tk1;
     const bool warp_has_rows = rowbase / a.rpt < ntok;
+    const int w_lo_last = ma_first_key(a.mask_kind, a.mask_size, w_hi);          // the last row's first key: the largest
+    const bool w_all_rows = (rowbase + 15) / a.rpt < ntok && nheads == a.rpt;    // all 16 rows are real
 
     for (int tile = t0; tile < t1; ++tile) {
         const int it = tile - t0;
-        if (tile + 1 < t1) load_tile(tile + 1, (it + 1) & 1);
+        if (tile + STAGES - 1 < t1) load_tile(tile + STAGES - 1, (it + STAGES - 1) % STAGES);
         cp_async_commit();
-        cp_async_wait<1>();
+        cp_async_wait<STAGES - 1>();
         __syncthreads();
-        const __nv_bfloat16* Ks = KV + (size_t)(it & 1) * (k_elems + v_elems);
+        const __nv_bfloat16* Ks = KV + (size_t)(it % STAGES) * (k_elems + v_elems);
         const __nv_bfloat16* Vs = V_IN_K ? Ks : Ks + k_elems;
         const int kfirst = tile * MA_TILE + keybase, klast = kfirst + NT * 8 - 1;
         if (warp_has_rows && kfirst <= w_hi && klast >= w_lo) {
@@ -192,17 +227,29 @@ attn_masked_kernel(const MaskedAttn a) {
             }
             const int key0 = kfirst + (lane & 3) * 2;
             float mx[2] = {-INFINITY, -INFINITY};
+            // only a tile that crosses some row's first or last visible key (or a warp with unused rows) needs the mask
+            if (!w_all_rows || kfirst < w_lo_last || klast > pos0 + w_tk0) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
+                for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + nt * 8 + (e & 1);
-                    const int rr = e >> 1;
-                    const bool vis = ok_row[rr] && key <= p_row[rr] && key >= lo_row[rr];
-                    const float v = vis ? s[nt][e] * a.scale_log2 : -INFINITY;
-                    s[nt][e] = v;
-                    mx[rr] = fmaxf(mx[rr], v);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + nt * 8 + (e & 1);
+                        const int rr = e >> 1;
+                        const bool vis = ok_row[rr] && key <= p_row[rr] && key >= lo_row[rr];
+                        const float v = vis ? s[nt][e] * a.scale_log2 : -INFINITY;
+                        s[nt][e] = v;
+                        mx[rr] = fmaxf(mx[rr], v);
+                    }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float v = s[nt][e] * a.scale_log2;
+                        s[nt][e] = v;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                    }
+            }
             float corr[2], mu[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
@@ -283,6 +330,7 @@ attn_masked_kernel(const MaskedAttn a) {
         return;
     }
     // SPLITK: the four warps' partial results of the same 16 rows, merged through shared memory
+    __syncthreads();             // every thread's copies have landed before the buffers are used for something else
     float* sm_o = reinterpret_cast<float*>(smem_raw);            // [4][16][DVP]
     float* sm_ml = sm_o + 4 * 16 * DVP;                          // [4][16][2]
 #pragma unroll
@@ -307,7 +355,8 @@ attn_masked_kernel(const MaskedAttn a) {
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
-        if (a.sink != nullptr) M = fmaxf(M, load_param(a.sink, a.sink_bf16, head0 + hh) * LOG2E);
+        const bool last = a.nsplit <= 1;                 // no other CTA shares these keys: finish here, sink included
+        if (last && a.sink != nullptr) M = fmaxf(M, load_param(a.sink, a.sink_bf16, head0 + hh) * LOG2E);
         const float Mu = M == -INFINITY ? 0.f : M;
         float L = 0.f, x0 = 0.f, x1 = 0.f;
 #pragma unroll
@@ -317,10 +366,44 @@ attn_masked_kernel(const MaskedAttn a) {
             x0 += sm_o[(w * 16 + r) * DVP + d] * f;
             x1 += sm_o[(w * 16 + r) * DVP + d + 1] * f;
         }
+        if (!last) {                                     // partial result of this CTA's keys, for the merge kernel
+            const size_t slot = ((size_t)(s0 + tk) * a.nh + head0 + hh) * a.nsplit + blockIdx.x;
+            a.part_o[slot * a.dv + d] = x0;
+            a.part_o[slot * a.dv + d + 1] = x1;
+            if (d == 0) {
+                a.part_ml[slot * 2] = M;
+                a.part_ml[slot * 2 + 1] = L;
+            }
+            continue;
+        }
         if (a.sink != nullptr) L += ma_exp2(load_param(a.sink, a.sink_bf16, head0 + hh) * LOG2E - Mu);
         const float inv = L > 0.f ? 1.f / L : 0.f;
         __nv_bfloat16* orow = a.out + (size_t)(s0 + q0 + tk) * a.out_stride + (size_t)(head0 + hh) * a.dv;
         *reinterpret_cast<uint32_t*>(orow + d) = pack_bf16(x0 * inv, x1 * inv);
+    }
+}
+
+// out[t, h, :] = sum_s o_s 2^(m_s - M) / (sum_s l_s 2^(m_s - M) + 2^(sink_h - M)) over the key splits' partial results
+__global__ void attn_masked_merge_kernel(const float* __restrict__ part_o_, const float* __restrict__ part_ml_, int nsplit,
+                                         int dv, int nh, const void* __restrict__ sink, int sink_bf16,
+                                         __nv_bfloat16* __restrict__ out, long long out_stride) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x / nh, h = blockIdx.x % nh;
+    const float* po = pdl_fresh(part_o_) + (size_t)blockIdx.x * nsplit * dv;
+    const float* pml = pdl_fresh(part_ml_) + (size_t)blockIdx.x * nsplit * 2;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, pml[2 * s]);
+    const float sk = sink != nullptr ? load_param(sink, sink_bf16, h) * 1.4426950408889634f : -INFINITY;
+    M = fmaxf(M, sk);
+    const float Mu = M == -INFINITY ? 0.f : M;
+    float L = ma_exp2(sk - Mu);
+    for (int s = 0; s < nsplit; ++s) L += pml[2 * s + 1] * ma_exp2(pml[2 * s] - Mu);
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < nsplit; ++s) acc += po[(size_t)s * dv + d] * ma_exp2(pml[2 * s] - Mu);
+        out[(size_t)t * out_stride + (size_t)h * dv + d] = __float2bfloat16_rn(acc * inv);
     }
 }
 
@@ -329,14 +412,19 @@ static int launch_masked(const MaskedAttn& a, int S, int max_q_len, cudaStream_t
     const int kstride = a.dkp + 8, vstride = DVP + 8;
     // V_IN_K: the value fragments of the padded columns dv .. DVP - 1 (never stored) may be read past a key row's
     // end, for the last row of the last stage past the tile: DVP spare elements keep that inside the allocation
-    size_t smem = (size_t)(MA_ROWS * kstride + 2 * (MA_TILE * kstride + (V_IN_K ? 0 : MA_TILE * vstride)) + (V_IN_K ? DVP : 0)) *
+    constexpr int STAGES = SPLITK ? 3 : 2;
+    size_t smem = (size_t)((SPLITK ? 16 : MA_ROWS) * kstride + STAGES * (MA_TILE * kstride + (V_IN_K ? 0 : MA_TILE * vstride)) + (V_IN_K ? DVP : 0)) *
                   sizeof(__nv_bfloat16);
     if (SPLITK) smem = std::max(smem, (size_t)(4 * 16 * DVP + 4 * 16 * 2) * sizeof(float));
     if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
     auto kern = attn_masked_kernel<DVP, V_IN_K, SPLITK>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    dim3 grid((max_q_len + a.tok_per_cta - 1) / a.tok_per_cta, a.nkv * a.hgroups, S);
-    return (int)launch_kernel(kern, grid, dim3(MA_THREADS), smem, stream, a);
+    dim3 grid(SPLITK ? a.nsplit : (max_q_len + a.tok_per_cta - 1) / a.tok_per_cta, a.nkv * a.hgroups, S);
+    const cudaError_t rc = launch_kernel(kern, grid, dim3(MA_THREADS), smem, stream, a);
+    if (rc != cudaSuccess || !SPLITK || a.nsplit <= 1) return (int)rc;
+    return (int)launch_kernel(attn_masked_merge_kernel, dim3(S * a.nh), dim3(a.dv >= 128 ? 128 : 64), 0, stream,
+                              (const float*)a.part_o, (const float*)a.part_ml, a.nsplit, a.dv, a.nh, a.sink, a.sink_bf16,
+                              a.out, a.out_stride);
 }
 
 }  // namespace prism
@@ -349,7 +437,9 @@ PRISM_EXPORT int prism_attention_masked_supported(int dk, int dv, int nh, int nk
 
 // q [T, nh, dk] bf16 (token and head strides in elements, multiples of 8); out [T, nh * dv]; planes as for
 // prism_attention_masked_generic; vc == nullptr: the values are the first dv entries of the key rows.
-// few_rows != 0: every segment has one token and nh / nkv <= 16 (the launcher checks the latter).
+// few_rows != 0: every segment has one token and nh / nkv <= 16 (the launcher checks the latter); then nsplit
+// CTAs share the key tiles of one (segment, kv head), and for nsplit > 1 leave partial results in part_o
+// [S, nh, nsplit, dv] and part_ml [S, nh, nsplit, 2] (float32) for a merge kernel.
 PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, int q_head_stride, void* out,
                                              long long out_stride, const void* kc, long long k_row_stride,
                                              int k_head_stride, const void* vc, long long v_row_stride,
@@ -357,7 +447,8 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
                                              const int* seg_start, const int* cached_len, int S, int max_q_len,
                                              int nh, int nkv, int dk, int dv, int page_size, int num_pages,
                                              int mask_kind, int mask_size, float scale, const void* sink,
-                                             int sink_dtype, int few_rows, int* err, cudaStream_t stream) {
+                                             int sink_dtype, int few_rows, int nsplit, float* part_o, float* part_ml,
+                                             int* err, cudaStream_t stream) {
     using namespace prism;
     if (S <= 0 || max_q_len <= 0) return 0;
     if (!prism_attention_masked_supported(dk, dv, nh, nkv)) return (int)cudaErrorInvalidValue;
@@ -367,7 +458,9 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
         (mask_kind != PRISM_MASK_CAUSAL && mask_size < 1))
         return (int)cudaErrorInvalidValue;
     const int rep = nh / nkv;
-    if (few_rows && (rep > 16 || max_q_len != 1)) return (int)cudaErrorInvalidValue;
+    if (few_rows && (rep > 16 || max_q_len != 1 || nsplit < 1 || nsplit > 65535 ||
+                     (nsplit > 1 && (part_o == nullptr || part_ml == nullptr))))
+        return (int)cudaErrorInvalidValue;
     MaskedAttn a;
     a.q = (const __nv_bfloat16*)q; a.q_stride = q_stride; a.q_head_stride = q_head_stride;
     a.out = (__nv_bfloat16*)out; a.out_stride = out_stride;
@@ -380,6 +473,12 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
     a.rpt = rep < MA_ROWS ? rep : MA_ROWS;
     a.tok_per_cta = MA_ROWS / a.rpt;
     a.hgroups = (rep + MA_ROWS - 1) / MA_ROWS;
+    a.page_shift = -1;
+    if (page_size > 0 && (page_size & (page_size - 1)) == 0)
+        for (a.page_shift = 0; (1 << a.page_shift) < page_size;) ++a.page_shift;
+    a.nsplit = few_rows ? nsplit : 1;
+    a.part_o = part_o;
+    a.part_ml = part_ml;
 #define PRISM_MA_LAUNCH(DVP)                                                                                        \
     do {                                                                                                            \
         if (v_in_k) return few_rows ? launch_masked<DVP, true, true>(a, S, max_q_len, stream)                       \

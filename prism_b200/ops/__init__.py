@@ -94,7 +94,7 @@ class _Sig:
                                       _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _p]
     prism_attention_masked_supported = [_i, _i, _i, _i]
     prism_attention_masked_bf16 = [_p, _ll, _i, _p, _ll, _p, _ll, _i, _p, _ll, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
-                                   _i, _i, _i, _i, _f, _p, _i, _i, _p, _p]
+                                   _i, _i, _i, _i, _f, _p, _i, _i, _i, _p, _p, _p, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_rotate_slice = [_p, _ll, _i, _p, _ll, _i, _i, _i, _i, _p, _p, _i, _i, _p]
@@ -1273,14 +1273,29 @@ def masked_attention(ctx, q: torch.Tensor, out: torch.Tensor, k_plane: torch.Ten
     if (q.dtype == torch.bfloat16 and MASKED_TC and not FORCE_GENERIC_ATTENTION
             and attention_masked_tc_ok(q, k_plane, v_plane, nh, nkv, dk, dv)):
         few = ctx.decode_only and nh // nkv <= 16
+        ns = masked_decode_splits(ctx.S, nkv, mask.most_keys(ctx.max_kv_len)) if few else 1
         attention_masked_bf16(q, out, k_plane, v_plane, block_table, ctx.seg_start, ctx.cached_len, ctx.S,
-                              ctx.max_q_len, num_pages, mask, scale, sink, few, ctx.err)
+                              ctx.max_q_len, num_pages, mask, scale, sink, few, ctx.err, nsplit=ns)
         return
     attention_masked_generic(q, out, k_plane, v_plane, block_table, ctx.positions, ctx.tok_seg, num_pages, mask,
                              scale, sink, ctx.err)
 
 
 MASKED_TC = os.environ.get("PRISM_MASKED_TC", "1") != "0"
+
+
+MASKED_DECODE_MIN_TILES = 2       # 64-key tiles a CTA keeps at least when a request's keys are shared among CTAs
+
+
+def masked_decode_splits(S: int, nkv: int, most_keys: int, sms: Optional[int] = None) -> int:
+    """CTAs that share one (request, kv head)'s keys in a decode step of the masked attention kernel: as many as
+    fill one wave of two CTAs per SM, none with fewer than ``MASKED_DECODE_MIN_TILES`` tiles.  ``most_keys``:
+    the most keys a request of the step can see (its mask's size, or the longest context)."""
+    if os.environ.get("PRISM_MASKED_SPLITS"):
+        return int(os.environ["PRISM_MASKED_SPLITS"])
+    tiles = most_keys // 64 + 1
+    fill = (2 * (sms or num_sms())) // max(1, S * nkv)
+    return max(1, min(fill, tiles // MASKED_DECODE_MIN_TILES, 64))
 
 
 def _values_in_keys(k_plane: torch.Tensor, v_plane: torch.Tensor) -> bool:
@@ -1304,9 +1319,10 @@ def attention_masked_tc_ok(q, k_plane, v_plane, nh: int, nkv: int, dk: int, dv: 
 
 def attention_masked_bf16(q, out, k_plane, v_plane, block_table, seg_start, cached_len, S: int, max_q_len: int,
                           num_pages: int, mask: KeyMask, scale: float, sink: Optional[torch.Tensor], few_rows: bool,
-                          err: torch.Tensor):
+                          err: torch.Tensor, nsplit: int = 1):
     """Tensor-core attention under a ``KeyMask`` with an optional sink; ``few_rows``: a decode step (one token
-    per segment, at most 16 query heads per kv head), where a CTA's four warps share the keys."""
+    per segment, at most 16 query heads per kv head), where a CTA's four warps share the keys and ``nsplit``
+    CTAs the key tiles of one (segment, kv head), merged by a second kernel."""
     _cuda(q, out, k_plane, v_plane, block_table, seg_start, cached_len, sink)
     T, nh, dk = q.shape
     P, nkv, dv = k_plane.shape[1], k_plane.shape[2], v_plane.shape[3]
@@ -1315,12 +1331,20 @@ def attention_masked_bf16(q, out, k_plane, v_plane, block_table, seg_start, cach
     krs, khs = _plane_strides(k_plane)
     vrs, vhs = _plane_strides(v_plane)
     vin = _values_in_keys(k_plane, v_plane)
+    po = pml = None
+    if few_rows and nsplit > 1:
+        po = torch.empty((S, nh, nsplit, dv), dtype=torch.float32, device=q.device)
+        pml = torch.empty((S, nh, nsplit, 2), dtype=torch.float32, device=q.device)
     _check(lib().prism_attention_masked_bf16(
         _ptr(q), q.stride(0) if T > 1 else nh * dk, q.stride(1) if nh > 1 else dk, _ptr(out),
         out.stride(0) if T > 1 else nh * dv, _ptr(k_plane), krs, khs, None if vin else _ptr(v_plane), vrs, vhs,
         _ptr(block_table), block_table.shape[1], _ptr(seg_start), _ptr(cached_len), S, int(max_q_len), nh, nkv, dk, dv,
         P, num_pages, mask.kind, mask.size, float(scale), _ptr(sink), F32 if sink is None else _dt(sink),
-        1 if few_rows else 0, _ptr(err), _stream()), "attention_masked_bf16")
+        1 if few_rows else 0, int(nsplit) if few_rows else 1, _ptr(po), _ptr(pml), _ptr(err), _stream()),
+        "attention_masked_bf16")
+    if few_rows and nsplit > 1:
+        global launch_count
+        launch_count += 1          # the merge kernel
 
 
 def feed_forward_hidden(ctx, x: torch.Tensor, up_w: Optional[torch.Tensor], kind: str, out: torch.Tensor,

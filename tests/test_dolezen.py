@@ -186,3 +186,14 @@ def test_plain_forward_ignores_what_the_masks_hide():
     la, lb = DP.forward(raw, w, a)[0], DP.forward(raw, w, b)[0]
     changed = [i for i in range(20) if not torch.equal(la[i], lb[i])]
     assert changed == [7, 8, 9, 10, 11]
+
+
+def test_key_splits_of_a_masked_decode_step():
+    """As many CTAs per (request, kv head) as fill one wave, each keeping two tiles or more; a mask bounds
+    the keys whatever the context."""
+    assert ops.masked_decode_splits(8, 4, 1024, sms=148) == 8               # 17 tiles: 8 CTAs of 2 or 3 tiles
+    assert ops.masked_decode_splits(8, 4, ops.KeyMask.window(512).most_keys(100000), sms=148) == 4
+    assert ops.masked_decode_splits(64, 8, 4096, sms=148) == 1              # 512 CTAs fill the GPU by themselves
+    assert ops.masked_decode_splits(1, 1, 40, sms=148) == 1                 # one tile
+    assert ops.masked_decode_splits(1, 1, 100000, sms=148) == 64
+    assert ops.KeyMask.causal().most_keys(777) == 777 and ops.KeyMask.chunk(200).most_keys(777) == 200

@@ -51,6 +51,7 @@ def paged_case(segs, nkv, dk, dv, page_size, dtype, seed, values_in_keys=False):
     vp = kp[..., :dv] if values_in_keys else vp.to(dtype).to(DEV)
     ctx = types.SimpleNamespace(positions=i32(pos), tok_seg=i32(tok_seg), seg_start=i32(seg_start), cached_len=i32(cached),
                                 S=len(segs), max_q_len=max(n for _, n in segs), decode_only=all(n == 1 for _, n in segs),
+                                max_kv_len=max(c + n for c, n in segs),
                                 err=torch.zeros(1, dtype=torch.int32, device=DEV))
     return ctx, kp, vp, bt.to(DEV), total_pages + 4, dense
 
@@ -116,6 +117,13 @@ def test_attention_under_a_mask_with_sink(shape, mask, kernel):
                           scale, sink)
     err = float((out.float().cpu() - ref).abs().max())
     assert err <= (3e-5 if dtype == torch.float32 else 2.5e-2), err
+    if kernel == "tc_decode" and few:
+        # the same with a request's key tiles shared among CTAs (more CTAs than some requests have tiles)
+        for ns in (2, 5):
+            out2 = torch.zeros_like(out)
+            ops.attention_masked_bf16(qd, out2, kp, vp, bt, ctx.seg_start, ctx.cached_len, ctx.S, ctx.max_q_len, npages, m,
+                                      scale, sd, True, ctx.err, nsplit=ns)
+            assert float((out2.float().cpu() - ref).abs().max()) <= 2.5e-2, ns
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
