@@ -14,9 +14,10 @@
 //
 // Two shapes of the same loop:
 //   * portions (SPLITK false): warp w owns rows 16 w .. 16 w + 15 and walks all 64 keys of a tile;
-//   * few rows (SPLITK true; a decode step: one token per segment, at most 16 heads per kv head): all four
-//     warps own the same 16 rows, warp w takes keys 16 w .. 16 w + 15 of every tile, and the four partial
-//     (max, sum, output) are merged through shared memory at the end.
+//   * few rows (SPLITK true; a decode step: one token per segment; a CTA takes up to 16 of the heads of a kv
+//     head): all four warps own the same 16 rows, warp w takes keys 16 w .. 16 w + 15 of every tile, and the
+//     four partial (max, sum, output) are merged through shared memory at the end; several CTAs may share the
+//     key tiles of one (segment, kv head), and a second kernel merges their partial results.
 // The order of additions for a position depends on its place in the CTA's row tile, i.e. on how the request
 // was cut into steps, only through float32 rounding.
 #include <algorithm>
@@ -25,7 +26,13 @@
 
 namespace prism {
 
-constexpr int MA_TILE = 64;
+#ifndef PRISM_MA_PORTION_TILE
+#define PRISM_MA_PORTION_TILE 32
+#endif
+// keys per tile: 64 in the few-rows shape (16 for each warp); in the portions shape 32, which with two stages
+// leaves room for three or four CTAs per SM instead of two
+constexpr int MA_TILE_DECODE = 64;
+constexpr int MA_TILE_PORTION = PRISM_MA_PORTION_TILE;
 constexpr int MA_THREADS = 128;
 constexpr int MA_ROWS = 64;
 
@@ -52,7 +59,8 @@ struct MaskedAttn {
     int* err;
     int rpt;           // rows per token: the query heads of one kv head (at most 64 of them per CTA)
     int tok_per_cta;   // 64 / rpt
-    int hgroups;       // CTAs that share the heads of one kv head when there are more than 64
+    int hgroups;       // CTAs that share the heads of one kv head when there are more than hrows
+    int hrows;         // query heads of one kv head a CTA takes at most: 64, in the few-rows shape 16
     int page_shift;    // log2(page_size), or -1
     int nsplit;        // few-rows shape: CTAs that share one (segment, kv head)'s key tiles
     float* part_o;     // [segments, nh, nsplit, dv]   their partial outputs (not normalised) ...
@@ -71,12 +79,12 @@ __device__ __forceinline__ float ma_exp2(float x) {      // 0 for -inf
     return y;
 }
 
-// 64 cache rows (keys first_key ..) of one kv head into ks[64][kstride] and, unless the values are read out of
-// the key rows, vs[64][vstride].  A row is `kchunks` (`vchunks`) 16-byte pieces, of which the first `kreal`
+// ROWS (32 or 64) cache rows (keys first_key ..) of one kv head into ks[ROWS][kstride] and, unless the values are
+// read out of the key rows, vs[ROWS][vstride].  A row is `kchunks` (`vchunks`) 16-byte pieces, of which the first `kreal`
 // (`vreal`) come from the plane and the rest are zero; keys outside [lo, hi] are zero rows.  Sixteen threads
 // share a row and a thread serves rows tid / 16 + 8 j: it first looks up the slots of its eight rows (eight
 // independent loads of the block table, in flight together), then issues the copies.
-template <bool WITH_V>
+template <bool WITH_V, int ROWS>
 __device__ __forceinline__ void ma_load_tile(__nv_bfloat16* ks, int kstride, int kchunks, int kreal,
                                              __nv_bfloat16* vs, int vstride, int vchunks, int vreal,
                                              const __nv_bfloat16* __restrict__ kplane, long long k_row_stride, size_t k_head_off,
@@ -84,9 +92,10 @@ __device__ __forceinline__ void ma_load_tile(__nv_bfloat16* ks, int kstride, int
                                              const int* __restrict__ bt, int first_key, int lo, int hi,
                                              int page_size, int page_shift, int num_pages, int* err, int tid) {
     const int rr = tid >> 4, cc = tid & 15;
-    long long slot[8];
+    constexpr int PASSES = ROWS / 8;
+    long long slot[PASSES];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < PASSES; ++j) {
         const int key = first_key + rr + 8 * j;
         slot[j] = -1;
         if (key >= lo && key <= hi) {
@@ -97,7 +106,7 @@ __device__ __forceinline__ void ma_load_tile(__nv_bfloat16* ks, int kstride, int
         }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < PASSES; ++j) {
         const int r = rr + 8 * j;
         const bool row_ok = slot[j] >= 0;
         const __nv_bfloat16* ksrc = kplane + (row_ok ? (size_t)slot[j] * (size_t)k_row_stride + k_head_off : 0);
@@ -116,11 +125,12 @@ __device__ __forceinline__ void ma_load_tile(__nv_bfloat16* ks, int kstride, int
 }
 
 template <int DVP, bool V_IN_K, bool SPLITK>
-__global__ void __launch_bounds__(MA_THREADS)
+__global__ void __launch_bounds__(MA_THREADS, (!SPLITK && DVP <= 128 && PRISM_MA_PORTION_TILE == 32) ? 3 : 1)
 attn_masked_kernel(const MaskedAttn a) {
     pdl_trigger();
     pdl_wait();
-    constexpr int NT = SPLITK ? 2 : 8;                 // 8-key score tiles per warp and key tile
+    constexpr int MA_TILE = SPLITK ? MA_TILE_DECODE : MA_TILE_PORTION;
+    constexpr int NT = SPLITK ? 2 : MA_TILE / 8;       // 8-key score tiles per warp and key tile
     constexpr int STAGES = SPLITK ? 3 : 2;             // a decode CTA has little to compute: more tiles in flight
     constexpr int QROWS = SPLITK ? 16 : MA_ROWS;       // query rows the CTA keeps in shared memory
     const int seg = blockIdx.z;
@@ -131,8 +141,8 @@ attn_masked_kernel(const MaskedAttn a) {
     if (q0 >= qlen) return;
     const int ntok = min(a.tok_per_cta, qlen - q0);
     const int rep = a.nh / a.nkv;
-    const int head0 = kvh * rep + hg * MA_ROWS;                           // head of a token's first row
-    const int nheads = min(a.rpt, rep - hg * MA_ROWS);                    // rows of a token that are real
+    const int head0 = kvh * rep + hg * a.hrows;                           // head of a token's first row
+    const int nheads = min(a.rpt, rep - hg * a.hrows);                    // rows of a token that are real
     const int pos0 = a.cached_len[seg] + q0;
     const int* bt = a.block_table + (size_t)seg * a.bt_width;
 
@@ -165,7 +175,7 @@ attn_masked_kernel(const MaskedAttn a) {
     }
     auto load_tile = [&](int tile, int stage) {
         __nv_bfloat16* ks = KV + (size_t)stage * (k_elems + v_elems);
-        ma_load_tile<!V_IN_K>(ks, kstride, a.dkp / 8, a.dk / 8, ks + k_elems, vstride, DVP / 8, (a.dv + 7) / 8, a.kc,
+        ma_load_tile<!V_IN_K, MA_TILE>(ks, kstride, a.dkp / 8, a.dk / 8, ks + k_elems, vstride, DVP / 8, (a.dv + 7) / 8, a.kc,
                               a.k_row_stride, (size_t)kvh * a.k_head_stride, a.vc, a.v_row_stride,
                               (size_t)kvh * a.v_head_stride, bt, tile * MA_TILE, lo, hi, a.page_size, a.page_shift,
                               a.num_pages, a.err, tid);
@@ -413,6 +423,7 @@ static int launch_masked(const MaskedAttn& a, int S, int max_q_len, cudaStream_t
     // V_IN_K: the value fragments of the padded columns dv .. DVP - 1 (never stored) may be read past a key row's
     // end, for the last row of the last stage past the tile: DVP spare elements keep that inside the allocation
     constexpr int STAGES = SPLITK ? 3 : 2;
+    constexpr int MA_TILE = SPLITK ? MA_TILE_DECODE : MA_TILE_PORTION;
     size_t smem = (size_t)((SPLITK ? 16 : MA_ROWS) * kstride + STAGES * (MA_TILE * kstride + (V_IN_K ? 0 : MA_TILE * vstride)) + (V_IN_K ? DVP : 0)) *
                   sizeof(__nv_bfloat16);
     if (SPLITK) smem = std::max(smem, (size_t)(4 * 16 * DVP + 4 * 16 * 2) * sizeof(float));
@@ -437,7 +448,7 @@ PRISM_EXPORT int prism_attention_masked_supported(int dk, int dv, int nh, int nk
 
 // q [T, nh, dk] bf16 (token and head strides in elements, multiples of 8); out [T, nh * dv]; planes as for
 // prism_attention_masked_generic; vc == nullptr: the values are the first dv entries of the key rows.
-// few_rows != 0: every segment has one token and nh / nkv <= 16 (the launcher checks the latter); then nsplit
+// few_rows != 0: every segment has one token; then nsplit
 // CTAs share the key tiles of one (segment, kv head), and for nsplit > 1 leave partial results in part_o
 // [S, nh, nsplit, dv] and part_ml [S, nh, nsplit, 2] (float32) for a merge kernel.
 PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, int q_head_stride, void* out,
@@ -458,7 +469,7 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
         (mask_kind != PRISM_MASK_CAUSAL && mask_size < 1))
         return (int)cudaErrorInvalidValue;
     const int rep = nh / nkv;
-    if (few_rows && (rep > 16 || max_q_len != 1 || nsplit < 1 || nsplit > 65535 ||
+    if (few_rows && (max_q_len != 1 || nsplit < 1 || nsplit > 65535 ||
                      (nsplit > 1 && (part_o == nullptr || part_ml == nullptr))))
         return (int)cudaErrorInvalidValue;
     MaskedAttn a;
@@ -470,9 +481,10 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
     a.nh = nh; a.nkv = nkv; a.dk = dk; a.dkp = (dk + 15) / 16 * 16; a.dv = dv; a.page_size = page_size;
     a.num_pages = num_pages; a.mask_kind = mask_kind; a.mask_size = mask_size;
     a.scale_log2 = scale * 1.4426950408889634f; a.sink = sink; a.sink_bf16 = sink_dtype == PRISM_DTYPE_BF16; a.err = err;
-    a.rpt = rep < MA_ROWS ? rep : MA_ROWS;
-    a.tok_per_cta = MA_ROWS / a.rpt;
-    a.hgroups = (rep + MA_ROWS - 1) / MA_ROWS;
+    a.hrows = few_rows ? 16 : MA_ROWS;
+    a.rpt = rep < a.hrows ? rep : a.hrows;
+    a.tok_per_cta = few_rows ? 1 : MA_ROWS / a.rpt;
+    a.hgroups = (rep + a.hrows - 1) / a.hrows;
     a.page_shift = -1;
     if (page_size > 0 && (page_size & (page_size - 1)) == 0)
         for (a.page_shift = 0; (1 << a.page_shift) < page_size;) ++a.page_shift;

@@ -1272,8 +1272,8 @@ def masked_attention(ctx, q: torch.Tensor, out: torch.Tensor, k_plane: torch.Ten
     nkv, dv = k_plane.shape[2], v_plane.shape[3]
     if (q.dtype == torch.bfloat16 and MASKED_TC and not FORCE_GENERIC_ATTENTION
             and attention_masked_tc_ok(q, k_plane, v_plane, nh, nkv, dk, dv)):
-        few = ctx.decode_only and nh // nkv <= 16
-        ns = masked_decode_splits(ctx.S, nkv, mask.most_keys(ctx.max_kv_len)) if few else 1
+        few = ctx.decode_only
+        ns = masked_decode_splits(ctx.S, nkv * (-(-(nh // nkv) // 16)), mask.most_keys(ctx.max_kv_len)) if few else 1
         attention_masked_bf16(q, out, k_plane, v_plane, block_table, ctx.seg_start, ctx.cached_len, ctx.S,
                               ctx.max_q_len, num_pages, mask, scale, sink, few, ctx.err, nsplit=ns)
         return
@@ -1288,7 +1288,8 @@ MASKED_DECODE_MIN_TILES = 2       # 64-key tiles a CTA keeps at least when a req
 
 
 def masked_decode_splits(S: int, nkv: int, most_keys: int, sms: Optional[int] = None) -> int:
-    """CTAs that share one (request, kv head)'s keys in a decode step of the masked attention kernel: as many as
+    """CTAs that share one (request, kv head)'s keys (``nkv``: kv heads times the groups of 16 query heads that
+    share one) in a decode step of the masked attention kernel: as many as
     fill one wave of two CTAs per SM, none with fewer than ``MASKED_DECODE_MIN_TILES`` tiles.  ``most_keys``:
     the most keys a request of the step can see (its mask's size, or the longest context)."""
     if os.environ.get("PRISM_MASKED_SPLITS"):
@@ -1321,8 +1322,8 @@ def attention_masked_bf16(q, out, k_plane, v_plane, block_table, seg_start, cach
                           num_pages: int, mask: KeyMask, scale: float, sink: Optional[torch.Tensor], few_rows: bool,
                           err: torch.Tensor, nsplit: int = 1):
     """Tensor-core attention under a ``KeyMask`` with an optional sink; ``few_rows``: a decode step (one token
-    per segment, at most 16 query heads per kv head), where a CTA's four warps share the keys and ``nsplit``
-    CTAs the key tiles of one (segment, kv head), merged by a second kernel."""
+    per segment), where a CTA takes up to 16 query heads of a kv head, its four warps share the keys and
+    ``nsplit`` CTAs the key tiles of one (segment, kv head), merged by a second kernel."""
     _cuda(q, out, k_plane, v_plane, block_table, seg_start, cached_len, sink)
     T, nh, dk = q.shape
     P, nkv, dv = k_plane.shape[1], k_plane.shape[2], v_plane.shape[3]

@@ -108,8 +108,6 @@ def test_attention_under_a_mask_with_sink(shape, mask, kernel):
         if not ops.attention_masked_tc_ok(qd, kp, vp, nh, nkv, dk, dv):
             pytest.skip("sizes that go to the shape-generic kernel")
         few = kernel == "tc_decode"
-        if few and nh // nkv > 16:
-            few = False                                # as ops.masked_attention decides
         ops.attention_masked_bf16(qd, out, kp, vp, bt, ctx.seg_start, ctx.cached_len, ctx.S, ctx.max_q_len, npages, m,
                                   scale, sd, few, ctx.err)
     assert int(ctx.err.item()) == 0
