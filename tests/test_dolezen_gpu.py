@@ -74,10 +74,10 @@ def plain_attention(q, dense, segs, nh, nkv, mask_fn, size, scale, sink):
 
 
 SHAPES = [  # nh, nkv, dk, dv, values in keys
-    (6, 6, 64, 32, False), (6, 2, 16, 24, False), (8, 1, 144, 128, True), (3, 1, 40, 32, True),
+    (6, 3, 64, 48, False), (6, 2, 16, 24, False), (8, 1, 160, 128, True), (3, 1, 40, 32, True),
     (4, 4, 32, 32, False), (20, 1, 96, 96, True), (2, 1, 24, 8, False), (5, 5, 8, 6, False), (70, 1, 48, 16, True),
 ]
-MASKS = [("window", 40), ("chunk", 50), ("window", 1), ("chunk", 7), ("causal", 0), ("window", 200)]
+MASKS = [("window", 44), ("chunk", 50), ("window", 1), ("chunk", 7), ("causal", 0), ("window", 230)]
 
 
 @pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "h%d_g%d_k%d_v%d_%s" % s)
@@ -125,7 +125,7 @@ def test_attention_under_a_mask_with_sink(shape, mask, kernel):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("kind, size", [("window", 40), ("chunk", 64), ("chunk", 50), ("window", 65), ("causal", 0)])
+@pytest.mark.parametrize("kind, size", [("window", 37), ("chunk", 64), ("chunk", 50), ("window", 65), ("causal", 0)])
 def test_one_key_that_stands_out_is_seen_exactly_when_the_mask_lets_it(dtype, kind, size):
     """Among hundreds of keys one is aligned with the query and carries a value of its own.  The query's
     output holds that value when the key is far away but visible, at a page's border, just inside a window
