@@ -65,7 +65,15 @@ CONFIG_Z = dict(architecture="Dolezen", vocab=64, width=32, norm=dict(eps=1e-6),
     layer("latent_attention", latent(1, 8, 8, 8, 8, 8, 1), 32),
     layer("attention", attn(1, 1, 8, 8, 3, kv_from=0), 32),
 ])
-CONFIGS = {"X": (CONFIG_X, 11, 8), "Y": (CONFIG_Y, 12, 64), "Z": (CONFIG_Z, 13, 16)}      # config, seed, page size
+# W: sizes that are multiples of nothing (no 16-byte piece anywhere): every kernel's scalar path, and the library
+# products on unaligned rows
+CONFIG_W = dict(architecture="Dolezen", vocab=77, width=52, norm=dict(eps=1e-6), embedding=dict(scale=1.7), layers=[
+    layer("attention", attn(3, 3, 12, 20, 10), 44),
+    layer("latent_attention", latent(3, 10, 6, 14, 10, 20, 9, dims=6), 44),
+    layer("attention", attn(3, 3, 12, 20, 10, kv_from=0), 30),
+    layer("latent_attention", latent(2, 6, 2, 5, 7, 9, None, dims=2), None),
+])
+CONFIGS = {"X": (CONFIG_X, 11, 8), "Y": (CONFIG_Y, 12, 64), "Z": (CONFIG_Z, 13, 16), "W": (CONFIG_W, 14, 8)}      # config, seed, page size
 
 
 def draw_weights(raw: dict, seed: int) -> dict:

@@ -125,13 +125,14 @@ def test_attention_under_a_mask_with_sink(shape, mask, kernel):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("vin", [False, True], ids=["own_values", "values_in_keys"])
 @pytest.mark.parametrize("kind, size", [("window", 37), ("chunk", 64), ("chunk", 50), ("window", 65), ("causal", 0)])
-def test_one_key_that_stands_out_is_seen_exactly_when_the_mask_lets_it(dtype, kind, size):
+def test_one_key_that_stands_out_is_seen_exactly_when_the_mask_lets_it(dtype, kind, size, vin):
     """Among hundreds of keys one is aligned with the query and carries a value of its own.  The query's
     output holds that value when the key is far away but visible, at a page's border, just inside a window
     or block - and none of it just outside - in a prompt's portion and in a decoded token, on every kernel."""
     from prism_b200 import ops
-    nh, nkv, dk, dv, page = 4, 2, 32, 16, 64
+    nh, nkv, dk, dv, page = (4, 1, 32, 16, 64) if vin else (4, 2, 32, 16, 64)
     m = {"window": ops.KeyMask.window, "chunk": ops.KeyMask.chunk, "causal": lambda n: ops.KeyMask.causal()}[kind](size)
     L = 330
     for qpos in (329, 320, 256, 200, 192, 128, 127, 65, 64, 63, 1, 0):
@@ -143,14 +144,15 @@ def test_one_key_that_stands_out_is_seen_exactly_when_the_mask_lets_it(dtype, ki
             visible = key >= lo
             for n_new in ((1, 7) if qpos >= 6 else (1,)):           # decoded alone, or last of a portion
                 c = qpos - n_new + 1
-                ctx, kp, vp, bt, npages, dense = paged_case([(c, n_new)], nkv, dk, dv, page, dtype, seed=1)
-                # overwrite: all keys small, the chosen key along e0; its value is the all-ones vector times 8
+                ctx, kp, vp, bt, npages, dense = paged_case([(c, n_new)], nkv, dk, dv, page, dtype, seed=1, values_in_keys=vin)
+                # overwrite: the chosen key lies along the key rows' last entry; its value is the all-ones vector
+                # times 8 (with the values inside the key rows: the row's leading entries)
                 row = bt[0, key // page].item(), key % page
                 kp[row[0], row[1]] = 0
-                kp[row[0], row[1], :, 0] = 30.0
                 vp[row[0], row[1]] = 8.0
+                kp[row[0], row[1], :, dk - 1] = 30.0
                 q = torch.zeros(n_new, nh, dk, dtype=dtype, device=DEV)
-                q[-1, :, 0] = 30.0
+                q[-1, :, dk - 1] = 30.0
                 out = torch.empty(n_new, nh * dv, dtype=dtype, device=DEV)
                 variants = ["generic"] + (["tc"] if dtype == torch.bfloat16 else [])
                 for variant in variants:
@@ -268,7 +270,7 @@ def test_small_kernels(dtype):
 # ---------------------------------------------------------------------------------------------------------
 
 LIMIT = {"float32": 2e-5, "bfloat16": 3e-2}
-LENGTHS = {"X": [1, 9, 40, 71, 130], "Y": [2, 65, 128, 200, 333], "Z": [1, 5, 33]}
+LENGTHS = {"X": [1, 9, 40, 71, 130], "Y": [2, 65, 128, 200, 333], "Z": [1, 5, 33], "W": [3, 26, 61]}
 
 
 def runner_for(folder, dtype, max_tokens, page_size, max_live=4):
@@ -282,7 +284,7 @@ def sequences(name):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["X", "Y", "Z"])
+@pytest.mark.parametrize("name", ["X", "Y", "Z", "W"])
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "small_portions", "mixed"])
 def test_cutting(name, dtype, mode):
     """Whole prompts, a decoded tail, portions (one schedule of twos and threes only), and mixed batches of up
