@@ -1,6 +1,6 @@
-// Store of a step's new rows into a paged cache plane [slots, width]: the row of the token at position p of
-// request seg goes to slot block_table[seg][p / page_size] * page_size + p % page_size.  For layers whose
-// keys and values differ in size (each plane gets its own call) or are not rotated.  A page id outside the
+// Store of a step's new rows into one or two paged cache planes [slots, width]: the row of the token at position
+// p of request seg goes to slot block_table[seg][p / page_size] * page_size + p % page_size.  For layers whose
+// keys and values differ in size (a plane each, of its own width, filled by the same launch) or are not rotated.  A page id outside the
 // pool or a position outside [0, max_pos) is reported and the row skipped.
 #include "common.cuh"
 #include "vec.cuh"
@@ -8,8 +8,22 @@
 namespace prism {
 
 template <typename T>
+__device__ __forceinline__ void copy_row(const T* __restrict__ src, T* __restrict__ dst, int width, int vec) {
+    if (vec) {
+        for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
+            float v[8];
+            load8(src + c, v);
+            store8(dst + c, v);
+        }
+        return;
+    }
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+}
+
+template <typename T>
 __global__ void cache_store_kernel(const T* __restrict__ src_in, long long src_stride, T* __restrict__ cache, int width,
-                                   const int* __restrict__ block_table, int bt_width,
+                                   const T* __restrict__ src2_in, long long src2_stride, T* __restrict__ cache2, int width2,
+                                   int vec2, const int* __restrict__ block_table, int bt_width,
                                    const int* __restrict__ positions, const int* __restrict__ tok_seg,
                                    int page_size, int num_pages, int max_pos, int vec, int* err) {
     pdl_trigger();
@@ -25,33 +39,33 @@ __global__ void cache_store_kernel(const T* __restrict__ src_in, long long src_s
         if (threadIdx.x == 0) report_error(err, PRISM_ERR_PAGE_RANGE);
         return;
     }
-    T* dst = cache + ((size_t)page * page_size + pos % page_size) * width;
-    if (vec) {
-        for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
-            float v[8];
-            load8(src + c, v);
-            store8(dst + c, v);
-        }
-        return;
-    }
-    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+    const size_t slot = (size_t)page * page_size + pos % page_size;
+    copy_row(src, cache + slot * width, width, vec);
+    if (cache2 != nullptr)
+        copy_row(pdl_fresh(src2_in) + (size_t)blockIdx.x * src2_stride, cache2 + slot * width2, width2, vec2);
 }
 
 }  // namespace prism
 
+// src2 / cache2 (null: none): a second plane of width2 entries a slot, filled from rows of its own.
 PRISM_EXPORT int prism_cache_store(const void* src, long long src_stride, void* cache, int dtype, int width,
+                                   const void* src2, long long src2_stride, void* cache2, int width2,
                                    const int* block_table, int bt_width, const int* positions, const int* tok_seg,
                                    int T, int page_size, int num_pages, int max_pos, int* err, cudaStream_t stream) {
     if (T <= 0 || width <= 0) return 0;
-    const int threads = width >= 2048 ? 256 : 128;
-    if (dtype == PRISM_DTYPE_BF16) {
-        const int vec = width % 8 == 0 && src_stride % 8 == 0 && (uintptr_t)src % 16 == 0 && (uintptr_t)cache % 16 == 0;
+    if (cache2 != nullptr && (src2 == nullptr || width2 <= 0)) return (int)cudaErrorInvalidValue;
+    const int threads = width + width2 >= 2048 ? 256 : 128;
+    const size_t al = dtype == PRISM_DTYPE_BF16 ? 16 : 32;
+    auto vec_ok = [&](const void* s, long long ss, const void* c, int w) {
+        return w % 8 == 0 && ss % 8 == 0 && (uintptr_t)s % al == 0 && (uintptr_t)c % al == 0 ? 1 : 0;
+    };
+    const int vec = vec_ok(src, src_stride, cache, width), vec2 = cache2 != nullptr ? vec_ok(src2, src2_stride, cache2, width2) : 0;
+    if (dtype == PRISM_DTYPE_BF16)
         return (int)prism::launch_kernel(prism::cache_store_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
-                                         (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)cache, width, block_table,
-                                         bt_width, positions, tok_seg, page_size, num_pages, max_pos, vec, err);
-    }
-    const int vec = width % 8 == 0 && src_stride % 8 == 0 && (uintptr_t)src % 32 == 0 && (uintptr_t)cache % 32 == 0;
+                                         (const __nv_bfloat16*)src, src_stride, (__nv_bfloat16*)cache, width,
+                                         (const __nv_bfloat16*)src2, src2_stride, (__nv_bfloat16*)cache2, width2, vec2,
+                                         block_table, bt_width, positions, tok_seg, page_size, num_pages, max_pos, vec, err);
     return (int)prism::launch_kernel(prism::cache_store_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)src,
-                                     src_stride, (float*)cache, width, block_table, bt_width, positions, tok_seg, page_size,
-                                     num_pages, max_pos, vec, err);
+                                     src_stride, (float*)cache, width, (const float*)src2, src2_stride, (float*)cache2, width2,
+                                     vec2, block_table, bt_width, positions, tok_seg, page_size, num_pages, max_pos, vec, err);
 }

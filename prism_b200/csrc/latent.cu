@@ -5,7 +5,8 @@
 //    are the latent; the last r entries are the key part that carries the position and is shared by all
 //    heads: its first `rot_dims` entries are rotated (entry i paired with i + rot_dims / 2, angle
 //    position * inv_freq[i]), the others pass.  Norm, angles and rotation in float32, one rounding at the
-//    store into the paged plane [slots, R + r].
+//    store into the paged plane [slots, R + r].  The same launch can norm the query latent of the token, which
+//    is another column block of the same down projection.
 //  * rotate_slice: the same rotation for a slice of `width` entries of every head of a [T, nh, ...] tensor,
 //    written to a slice of another tensor (the queries' rotated part, next to their absorbed part).
 //  * rms_rows: x / sqrt(mean(x^2) + eps) * weight for rows of a float32 matrix with a row stride of its own
@@ -20,10 +21,22 @@ __global__ void latent_kv_store_kernel(const float* __restrict__ x_in, long long
                                        int rot_dims, const float* __restrict__ inv_freq, T* __restrict__ cache,
                                        const int* __restrict__ block_table, int bt_width,
                                        const int* __restrict__ positions, const int* __restrict__ tok_seg,
-                                       int page_size, int num_pages, int max_pos, int* err) {
+                                       int page_size, int num_pages, int max_pos, int* err,
+                                       const float* __restrict__ xq_in, int q_rank, const void* __restrict__ q_weight,
+                                       int q_weight_bf16, T* __restrict__ q_out, long long q_out_stride) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[33];
+    if (q_out != nullptr) {         // the query latent of the same token (same row stride), normed, in the same launch
+        const float* xq = pdl_fresh(xq_in) + (size_t)blockIdx.x * x_stride;
+        float sq = 0.f;
+        for (int c = threadIdx.x; c < q_rank; c += blockDim.x) sq += xq[c] * xq[c];
+        sq = block_sum(sq, scratch);
+        const float invq = 1.f / sqrtf(sq / (float)q_rank + eps);
+        T* o = q_out + (size_t)blockIdx.x * q_out_stride;
+        for (int c = threadIdx.x; c < q_rank; c += blockDim.x)
+            o[c] = from_float<T>(xq[c] * invq * load_param(q_weight, q_weight_bf16, c));
+    }
     const float* x = pdl_fresh(x_in) + (size_t)blockIdx.x * x_stride;
     const int pos = positions[blockIdx.x];
     float ss = 0.f;
@@ -109,23 +122,29 @@ PRISM_EXPORT int prism_rms_rows(const float* x, long long x_stride, const void* 
                                      weight, wb, eps, (float*)out, out_stride, width);
 }
 
-// x: float32 [T, R + r] with row stride x_stride; cache: plane [slots, R + r] of `dtype`.
+// x: float32 [T, R + r] with row stride x_stride; cache: plane [slots, R + r] of `dtype`.  xq (null: none):
+// float32 [T, q_rank] with the same row stride (another column block of the same product), RMS-normed with
+// q_weight into q_out [T, q_rank] of `dtype` by the same launch.
 PRISM_EXPORT int prism_latent_kv_store(const float* x, long long x_stride, const void* weight, int weight_dtype,
                                        float eps, int R, int r, int rot_dims, const float* inv_freq, void* cache,
                                        int dtype, const int* block_table, int bt_width, const int* positions,
                                        const int* tok_seg, int T, int page_size, int num_pages, int max_pos, int* err,
-                                       cudaStream_t stream) {
+                                       const float* xq, int q_rank, const void* q_weight, int q_weight_dtype,
+                                       void* q_out, long long q_out_stride, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (R <= 0 || r < 0 || rot_dims < 0 || rot_dims > r || rot_dims % 2) return (int)cudaErrorInvalidValue;
-    const int wb = weight_dtype == PRISM_DTYPE_BF16;
+    if (q_out != nullptr && (xq == nullptr || q_weight == nullptr || q_rank <= 0)) return (int)cudaErrorInvalidValue;
+    const int wb = weight_dtype == PRISM_DTYPE_BF16, qwb = q_weight_dtype == PRISM_DTYPE_BF16;
     const int threads = R >= 1024 ? 256 : 128;
     if (dtype == PRISM_DTYPE_BF16)
         return (int)prism::launch_kernel(prism::latent_kv_store_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, x,
                                          x_stride, weight, wb, eps, R, r, rot_dims, inv_freq, (__nv_bfloat16*)cache,
-                                         block_table, bt_width, positions, tok_seg, page_size, num_pages, max_pos, err);
+                                         block_table, bt_width, positions, tok_seg, page_size, num_pages, max_pos, err, xq,
+                                         q_rank, q_weight, qwb, (__nv_bfloat16*)q_out, q_out_stride);
     return (int)prism::launch_kernel(prism::latent_kv_store_kernel<float>, dim3(T), dim3(threads), 0, stream, x, x_stride,
                                      weight, wb, eps, R, r, rot_dims, inv_freq, (float*)cache, block_table, bt_width,
-                                     positions, tok_seg, page_size, num_pages, max_pos, err);
+                                     positions, tok_seg, page_size, num_pages, max_pos, err, xq, q_rank, q_weight, qwb,
+                                     (float*)q_out, q_out_stride);
 }
 
 // in/out point at the slice's first entry of head 0 of token 0; strides in elements.

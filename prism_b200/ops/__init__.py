@@ -95,8 +95,9 @@ class _Sig:
     prism_attention_masked_supported = [_i, _i, _i, _i]
     prism_attention_masked_bf16 = [_p, _ll, _i, _p, _ll, _p, _ll, _i, _p, _ll, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
                                    _i, _i, _i, _i, _f, _p, _i, _i, _i, _p, _p, _p, _p]
-    prism_cache_store = [_p, _ll, _p, _i, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
-    prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
+    prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
+    prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _i,
+                             _p, _ll, _p]
     prism_rotate_slice = [_p, _ll, _i, _p, _ll, _i, _i, _i, _i, _p, _p, _i, _i, _p]
     prism_activation = [_p, _ll, _p, _ll, _i, _i, _i, _i, _p]
     prism_rms_rows = [_p, _ll, _p, _i, _f, _p, _ll, _i, _i, _i, _p]
@@ -1206,35 +1207,55 @@ def attention_masked_generic(q: torch.Tensor, out: torch.Tensor, k_plane: torch.
 
 
 def cache_store(src: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
-                tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor):
+                tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor,
+                src2: Optional[torch.Tensor] = None, plane2: Optional[torch.Tensor] = None):
     """Rows ``src [T, width]`` (row stride free) into the paged plane ``[pages, P, ...]`` (``width`` entries a
-    slot), each at its token's position."""
-    _cuda(src, plane, block_table, positions, tok_seg)
+    slot), each at its token's position; ``src2`` into ``plane2`` (a plane of another width with the same pages:
+    a layer's values beside its keys) in the same launch."""
+    _cuda(src, plane, block_table, positions, tok_seg, src2, plane2)
     T, width = src.shape
     P = plane.shape[1]
     assert plane.is_contiguous() and plane[0, 0].numel() == width and plane.dtype == src.dtype and src.stride(1) == 1
+    width2 = 0
+    if plane2 is not None:
+        width2 = src2.shape[1]
+        assert plane2.is_contiguous() and plane2[0, 0].numel() == width2 and plane2.dtype == src.dtype
+        assert src2.stride(1) == 1 and src2.shape[0] == T and plane2.shape[:2] == plane.shape[:2]
     _check(lib().prism_cache_store(_ptr(src), src.stride(0) if T > 1 else width, _ptr(plane), _dt(src), width,
-                                   _ptr(block_table), block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, P,
+                                   _ptr(src2), 0 if src2 is None else (src2.stride(0) if T > 1 else width2), _ptr(plane2),
+                                   width2, _ptr(block_table), block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, P,
                                    num_pages, int(max_pos), _ptr(err), _stream()), "cache_store")
 
 
 def latent_kv_store(x: torch.Tensor, weight: torch.Tensor, eps: float, rank: int, rot_dims: int,
                     inv_freq: Optional[torch.Tensor], plane: torch.Tensor, block_table: torch.Tensor,
-                    positions: torch.Tensor, tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor):
+                    positions: torch.Tensor, tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor,
+                    xq: Optional[torch.Tensor] = None, q_weight: Optional[torch.Tensor] = None,
+                    q_out: Optional[torch.Tensor] = None):
     """The cache row of latent attention from its down projection ``x [T, rank + r]`` (float32): the first
     ``rank`` entries RMS-normed with ``weight``, the last ``r`` with their first ``rot_dims`` entries rotated
-    by the token's position; stored at the token's slot of ``plane [pages, P, 1, rank + r]``."""
-    _cuda(x, weight, inv_freq, plane, block_table, positions, tok_seg)
+    by the token's position; stored at the token's slot of ``plane [pages, P, 1, rank + r]``.  ``xq [T, q_rank]``
+    (float32, another column block of the same matrix as ``x``): RMS-normed with ``q_weight`` into ``q_out`` by the
+    same launch."""
+    _cuda(x, weight, inv_freq, plane, block_table, positions, tok_seg, xq, q_weight, q_out)
     T, width = x.shape
     r = width - rank
     assert x.dtype == torch.float32 and x.stride(1) == 1 and weight.shape == (rank,) and weight.is_contiguous()
     assert plane.is_contiguous() and plane[0, 0].numel() == width
     if rot_dims:
         assert inv_freq.dtype == torch.float32 and inv_freq.shape[0] * 2 == rot_dims
+    q_rank = 0
+    if q_out is not None:
+        q_rank = xq.shape[1]
+        assert xq.dtype == torch.float32 and xq.stride(1) == 1 and xq.shape[0] == T and (T == 1 or xq.stride(0) == x.stride(0))
+        assert q_weight.shape == (q_rank,) and q_weight.is_contiguous() and q_out.shape == (T, q_rank)
+        assert q_out.stride(1) == 1 and q_out.dtype == plane.dtype
     _check(lib().prism_latent_kv_store(_ptr(x), x.stride(0) if T > 1 else width, _ptr(weight), _dt(weight), float(eps),
                                        rank, r, int(rot_dims), _ptr(inv_freq), _ptr(plane), _dt(plane), _ptr(block_table),
                                        block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, plane.shape[1], num_pages,
-                                       int(max_pos), _ptr(err), _stream()), "latent_kv_store")
+                                       int(max_pos), _ptr(err), _ptr(xq), q_rank, _ptr(q_weight),
+                                       F32 if q_weight is None else _dt(q_weight), _ptr(q_out),
+                                       0 if q_out is None else q_out.stride(0), _stream()), "latent_kv_store")
 
 
 def rotate_slice(src: torch.Tensor, dst: torch.Tensor, rot_dims: int, inv_freq: Optional[torch.Tensor],

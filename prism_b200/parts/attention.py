@@ -173,9 +173,7 @@ class GQAAttention(Mixer):
                     ops.rotate_slice(k, k, rot.rotary_dim, rot.inv_freq, ctx.positions)
         if self.own_kv:
             ops.cache_store(qkv[:, qs:qs + kvs], cache.k, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages,
-                            ctx.max_positions, ctx.err)
-            ops.cache_store(qkv[:, qs + kvs:], cache.v, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages,
-                            ctx.max_positions, ctx.err)
+                            ctx.max_positions, ctx.err, src2=qkv[:, qs + kvs:], plane2=cache.v)
         ops.masked_attention(ctx, q, out, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
                              self.w.get("sink"))
 
@@ -292,10 +290,10 @@ class LatentAttention(Mixer):
         # both down projections in one product; float32, because each feeds a norm
         down = ops.linear(x, self.w["down_w"], None, out_dtype=torch.float32)
         cq = ctx.alloc((T, self.q_rank), x.dtype)
-        ops.rms_rows(down[:, :self.q_rank], self.w["dq_norm"], self.eps, cq)
+        # one launch: the query latent normed, the key/value latent normed, the shared key part rotated, the row stored
         ops.latent_kv_store(down[:, self.q_rank:], self.w["dkv_norm"], self.eps, R, self.rope_dims, self.inv_freq,
                             cache.k, cache.block_table, ctx.positions, ctx.tok_seg, cache.num_pages, ctx.max_positions,
-                            ctx.err)
+                            ctx.err, xq=down[:, :self.q_rank], q_weight=self.w["dq_norm"], q_out=cq)
         q = ops.linear(cq, self.w["uq_w"]).view(T, nh, hd + rd)
         qf = ctx.alloc((T, nh, R + rd), x.dtype)                   # per head [plain part in latent space | rotated part]
         ops.matmul_heads(q[:, :, :hd], self.uk_t, qf[:, :, :R])

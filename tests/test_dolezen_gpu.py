@@ -75,7 +75,7 @@ def plain_attention(q, dense, segs, nh, nkv, mask_fn, size, scale, sink):
 
 SHAPES = [  # nh, nkv, dk, dv, values in keys
     (6, 3, 64, 48, False), (6, 2, 16, 24, False), (8, 1, 160, 128, True), (3, 1, 40, 32, True),
-    (4, 4, 32, 32, False), (20, 1, 96, 96, True), (2, 1, 24, 8, False), (5, 5, 8, 6, False), (70, 1, 48, 16, True),
+    (4, 4, 32, 32, False), (20, 1, 96, 96, True), (4, 1, 320, 288, True), (2, 1, 24, 8, False), (5, 5, 8, 6, False), (70, 1, 48, 16, True),
 ]
 MASKS = [("window", 44), ("chunk", 50), ("window", 1), ("chunk", 7), ("causal", 0), ("window", 230)]
 
@@ -206,8 +206,15 @@ def test_latent_cache_row_and_query_rotation(dtype, R, r, dims):
     plane = torch.zeros(8, page, 1, R + r, dtype=dtype, device=DEV)
     inv = (50.0 ** (-2.0 * torch.arange(dims // 2, dtype=torch.float64) / max(dims, 1))).float().to(DEV)
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
-    ops.latent_kv_store(x.to(DEV)[:, 5:], w.to(DEV), 1e-5, R, dims, inv, plane, bt, i32(pos), i32([0] * T), 8, 1 << 20, err)
+    wq = (torch.randn(5, generator=g) * 0.2 + 1).to(dtype)
+    cq = torch.zeros(T, 7, dtype=dtype, device=DEV)
+    xd = x.to(DEV)
+    ops.latent_kv_store(xd[:, 5:], w.to(DEV), 1e-5, R, dims, inv, plane, bt, i32(pos), i32([0] * T), 8, 1 << 20, err,
+                        xq=xd[:, :5], q_weight=wq.to(DEV), q_out=cq[:, 1:6])
     assert int(err.item()) == 0
+    # the query latent (the matrix's first columns), normed by the same launch into a strided output
+    assert torch.allclose(cq[:, 1:6].float().cpu(), DP.rms_norm(x[:, :5], wq.float(), 1e-5), atol=1e-5 if dtype == torch.float32 else 3e-2)
+    assert float(cq[:, 0].abs().max()) == 0 and float(cq[:, 6].abs().max()) == 0
     c = DP.rms_norm(x[:, 5:5 + R], w.float(), 1e-5)
     kr = DP.rotate(x[:, 5 + R:], torch.tensor(pos), 50.0, dims) if r else x[:, 5 + R:]
     tol = 1e-5 if dtype == torch.float32 else 2e-2
@@ -263,6 +270,14 @@ def test_small_kernels(dtype):
     for t, (pg, sl) in enumerate([(4, 7), (1, 0), (0, 0), (2, 7)]):
         assert torch.equal(plane[pg, sl].reshape(-1), src[t, 9:21])
     assert int((plane != 0).sum()) <= 48 and int(e.item()) == 0
+    # two planes of different widths in one launch
+    plane.zero_()
+    plane2 = torch.zeros(5, 8, 2, 4, dtype=dtype, device=DEV)
+    ops.cache_store(src[:, 9:21], plane, bt, torch.tensor([7, 8, 0, 15], dtype=torch.int32, device=DEV),
+                    torch.tensor([0, 0, 1, 1], dtype=torch.int32, device=DEV), 5, 100, e, src2=src[:, 21:29], plane2=plane2)
+    for t, (pg, sl) in enumerate([(4, 7), (1, 0), (0, 0), (2, 7)]):
+        assert torch.equal(plane[pg, sl].reshape(-1), src[t, 9:21]) and torch.equal(plane2[pg, sl].reshape(-1), src[t, 21:29])
+    assert int((plane2 != 0).sum()) <= 32 and int(e.item()) == 0
 
 
 # ---------------------------------------------------------------------------------------------------------
