@@ -46,9 +46,6 @@ class GQAAttention(Mixer):
                  own_kv: bool = True, cache_chunk="mask", names: Optional[dict] = None):
         if num_heads % num_kv_heads:
             raise ConfigError(f"num_heads {num_heads} not divisible by num_kv_heads {num_kv_heads}")
-        if not 2 <= int(head_dim) <= MAX_HEAD_DIM or int(head_dim) % 2:
-            raise ConfigError(f"head_dim {head_dim}: the attention kernels take even head sizes from 2 to "
-                              f"{MAX_HEAD_DIM}")
         self.hidden_size, self.nh, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
         self.qkv_bias, self.o_bias = bool(qkv_bias), bool(o_bias)
         self.window = None if window is None else int(window)
@@ -67,6 +64,14 @@ class GQAAttention(Mixer):
         # projection, (rotation,) one store per plane, attention under a KeyMask
         self.general = self.vhd != self.hd or self.chunk is not None or self.sink or not self.own_kv
         self._own_in = self._own_out = True
+        # the equal-size kernels keep a head's row in a warp's registers and rotate pairs; the general path takes
+        # any key size (its kernels loop over it) and values of up to 1024 entries
+        if not self.general and (not 2 <= self.hd <= MAX_HEAD_DIM or self.hd % 2):
+            raise ConfigError(f"head_dim {head_dim}: the attention kernels take even head sizes from 2 to "
+                              f"{MAX_HEAD_DIM}")
+        if self.general and (self.hd < 1 or self.vhd > 1024):
+            raise ConfigError(f"head_dim {head_dim}, value size {self.vhd}: keys need at least one entry and values "
+                              f"at most 1024")
         self.mask = ops.KeyMask.chunk(self.chunk) if self.chunk is not None else ops.KeyMask.window(self.window)
 
     @property

@@ -349,6 +349,9 @@ ONE_LAYER = {
     "latent": one_layer("latent_attention", latent(4, 16, 16, 16, 24, 32, 12, base=300.0)),
     "latent_part_rotated": one_layer("latent_attention", latent(2, 8, 24, 40, 16, 16, 30, dims=4)),
     "feed_forward": one_layer("attention", attn(1, 1, 8, 8, 1), ff=112),
+    "odd_sizes": one_layer("attention", attn(2, 1, 7, 5, 6), ff=33, width=37, vocab=51),
+    "wide_heads": one_layer("attention", attn(2, 2, 272, 264, 40), width=64),
+    "latent_odd": one_layer("latent_attention", latent(3, 5, 6, 7, 9, 11, 4, dims=2), width=29, vocab=40),
 }
 
 
