@@ -26,6 +26,9 @@
 
 namespace prism {
 
+#ifndef PRISM_MA_PORTION_STAGES
+#define PRISM_MA_PORTION_STAGES 2
+#endif
 #ifndef PRISM_MA_PORTION_TILE
 #define PRISM_MA_PORTION_TILE 32
 #endif
@@ -131,7 +134,7 @@ attn_masked_kernel(const MaskedAttn a) {
     pdl_wait();
     constexpr int MA_TILE = SPLITK ? MA_TILE_DECODE : MA_TILE_PORTION;
     constexpr int NT = SPLITK ? 2 : MA_TILE / 8;       // 8-key score tiles per warp and key tile
-    constexpr int STAGES = SPLITK ? 3 : 2;             // a decode CTA has little to compute: more tiles in flight
+    constexpr int STAGES = SPLITK ? 3 : PRISM_MA_PORTION_STAGES;   // a decode CTA has little to compute: more tiles in flight
     constexpr int QROWS = SPLITK ? 16 : MA_ROWS;       // query rows the CTA keeps in shared memory
     const int seg = blockIdx.z;
     const int kvh = blockIdx.y / a.hgroups, hg = blockIdx.y % a.hgroups;
@@ -422,7 +425,7 @@ static int launch_masked(const MaskedAttn& a, int S, int max_q_len, cudaStream_t
     const int kstride = a.dkp + 8, vstride = DVP + 8;
     // V_IN_K: the value fragments of the padded columns dv .. DVP - 1 (never stored) may be read past a key row's
     // end, for the last row of the last stage past the tile: DVP spare elements keep that inside the allocation
-    constexpr int STAGES = SPLITK ? 3 : 2;
+    constexpr int STAGES = SPLITK ? 3 : PRISM_MA_PORTION_STAGES;
     constexpr int MA_TILE = SPLITK ? MA_TILE_DECODE : MA_TILE_PORTION;
     size_t smem = (size_t)((SPLITK ? 16 : MA_ROWS) * kstride + STAGES * (MA_TILE * kstride + (V_IN_K ? 0 : MA_TILE * vstride)) + (V_IN_K ? DVP : 0)) *
                   sizeof(__nv_bfloat16);
