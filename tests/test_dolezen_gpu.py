@@ -396,3 +396,37 @@ def test_greedy_generation_through_the_scheduler():
                 seq.append(tok)
             assert len(r.token_ids) == n_new
         assert eng.cache.pages_in_use() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_replay_program_serves_the_design(tmp_path, dtype):
+    """bin/trace_run as a user runs it, on a Dolezen folder: the model class is found by config.json, the pool
+    holds what --max-tokens says, steps come as JSON lines and logits leave as <step>.f32 files."""
+    import json
+    import os
+    import subprocess
+    import sys
+    import numpy as np
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "X"
+    vocab = CONFIGS[name][0]["vocab"]
+    seqs = {f"q{i}": random_tokens(vocab, n, 500 + i) for i, n in enumerate([70, 33, 90, 12, 64, 5])}
+    steps = trace_mixed(seqs, seed=17)
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model_folder(name), "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", str(trace_budget(steps, 64))],
+                          input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    got, fed = {}, {}
+    for s in steps:
+        n_want = sum(len(e["want"]) for e in s["entries"])
+        data = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(n_want, vocab)
+        r = 0
+        for e in s["entries"]:
+            for w in e["want"]:
+                got[(e["id"], fed.get(e["id"], 0) + w)] = torch.from_numpy(data[r].copy())
+                r += 1
+            fed[e["id"]] = fed.get(e["id"], 0) + len(e["tokens"])
+    assert len(got) == sum(len(s) for s in seqs.values())
+    compare(name, seqs, got, LIMIT[dtype])
