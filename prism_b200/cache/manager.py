@@ -47,23 +47,34 @@ class CacheGroup:
 def plan_groups(cache_needs: Sequence[Optional[CacheNeed]], reads: Sequence[Optional[int]]):
     """Group the cache planes of a model.  ``cache_needs[e]``: what schedule
     entry e owns (None if it reads entry ``reads[e]``'s plane, or needs
-    nothing).  Returns ``(groups, where)`` with ``where[e] = (group index,
-    plane index, owns)`` or None."""
+    nothing; a tuple of needs for a mixer that keeps several things).  Returns
+    ``(groups, where)`` with ``where[e] = (group index, plane index, owns)``
+    or None - for an entry with a tuple of needs, a list of such triples in
+    the order of the needs."""
     groups: List[CacheGroup] = []
     by_key: Dict[tuple, CacheGroup] = {}
-    where: List[Optional[Tuple[int, int, bool]]] = [None] * len(cache_needs)
-    for e, need in enumerate(cache_needs):
-        if need is None or need.kind == "none":
-            continue
+    where: list = [None] * len(cache_needs)
+
+    def place(e, need):
         g = by_key.get(need.group_key())
         if g is None:
             g = CacheGroup(len(groups), need)
             groups.append(g)
             by_key[need.group_key()] = g
-        where[e] = (g.index, len(g.entries), True)
         g.entries.append(e)
+        return (g.index, len(g.entries) - 1, True)
+
+    for e, need in enumerate(cache_needs):
+        if need is None:
+            continue
+        if isinstance(need, (tuple, list)):
+            where[e] = [place(e, n) for n in need if n.kind != "none"]
+        elif need.kind != "none":
+            where[e] = place(e, need)
     for e, src in enumerate(reads):
         if src is not None:
+            if isinstance(where[src], list):
+                raise ValueError(f"schedule entry {e} reads the cache of entry {src}, which keeps several things")
             gi, pi, _ = where[src]
             where[e] = (gi, pi, False)
     return groups, where
@@ -76,7 +87,8 @@ def pool_sizes(groups: Sequence[CacheGroup], page_size: int, elem_bytes: int, ma
     ``max_seqs`` requests of ``max_seq_len`` tokens hold and at least 16.  A group whose layers see a window (or a block of positions)
     needs, per request, the pages under the window and under one step's portion (``max_portion`` tokens)
     plus one - pages behind the window come back when the step is committed - so it gets that many for
-    every request slot, never more than the other groups."""
+    every request slot, never more than the other groups; the pages of the first positions that a window
+    keeps visible (``keep_first``) come on top."""
     P = int(page_size)
     cap = max_seqs * ((max_seq_len + P - 1) // P)
     page_bytes = {g.index: g.num_planes * P * g.need.num_kv_heads * (g.need.head_dim + g.need.value_dim) * elem_bytes
@@ -84,7 +96,7 @@ def pool_sizes(groups: Sequence[CacheGroup], page_size: int, elem_bytes: int, ma
     def span(need):          # the most keys a query of this group sees (None: all)
         sizes = [n for n in (need.window, need.chunk) if n is not None]
         return min(sizes) if sizes else None
-    windowed = {g.index: min(cap, max_seqs * ((span(g.need) + max_portion + P - 1) // P + 1))
+    windowed = {g.index: min(cap, max_seqs * ((span(g.need) + max_portion + P - 1) // P + 1 + (g.need.keep_first + P - 1) // P))
                 for g in groups if g.kind == "paged" and span(g.need) is not None}
     if num_pages:
         full = int(num_pages)
@@ -241,7 +253,9 @@ class CacheManager:
             # under a chunked mask those from the start of its own block
             first_visible = g.need.first_kept(rc.length)
             pages = rc.pages[g.index]
-            for idx in range(len(pages)):
+            # pages that hold any of the first positions a window keeps visible stay for good
+            kept = (g.need.keep_first + self.page_size - 1) // self.page_size
+            for idx in range(kept, len(pages)):
                 if (idx + 1) * self.page_size > first_visible:
                     break
                 if pages[idx] >= 0:

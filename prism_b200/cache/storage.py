@@ -73,16 +73,12 @@ class CacheStorage:
 
     def views(self, block_tables, slots_dev, host_slots) -> list:
         """Per schedule entry the view its mixer gets (None if it needs no cache)."""
-        out = []
-        for w in self.where:
-            if w is None:
-                out.append(None)
-                continue
+        def one(w):
             gi, plane, owns = w
             g = self.groups[gi]
             if g.kind == "paged":
-                out.append(PagedCacheView(self.k[gi][plane], self.v[gi][plane] if gi in self.v else None, block_tables[gi],
-                                          self.num_pages[gi] + 1, self.page_size, owns, g.need.window, gi))
-            else:
-                out.append(StateCacheView(self.state[gi][plane], slots_dev, host_slots, owns, gi))
-        return out
+                return PagedCacheView(self.k[gi][plane], self.v[gi][plane] if gi in self.v else None, block_tables[gi],
+                                      self.num_pages[gi] + 1, self.page_size, owns, g.need.window, gi)
+            return StateCacheView(self.state[gi][plane], slots_dev, host_slots, owns, gi)
+        # an entry whose mixer keeps several things gets a tuple of views, in the order of its needs
+        return [None if w is None else (tuple(one(x) for x in w) if isinstance(w, list) else one(w)) for w in self.where]

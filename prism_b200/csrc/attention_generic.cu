@@ -65,7 +65,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, int q
                                     int bt_width, const int* __restrict__ positions,
                                     const int* __restrict__ tok_seg, int Ttot, int nh, int nkv,
                                     int dk, int dv, int page_size, int num_pages, int mask_kind, int mask_size,
-                                    float scale, const void* __restrict__ sink, int sink_bf16, int* err) {
+                                    int mask_keep, float scale, const void* __restrict__ sink, int sink_bf16, int* err) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float smem[];
@@ -77,6 +77,9 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, int q
     const int pos = positions[t];
     const int* bt = block_table + (size_t)tok_seg[t] * bt_width;
     const int lo = mask_first_key(mask_kind, mask_size, pos);
+    // the first `mask_keep` positions stay visible behind a window: they are visited first, in blocks of 32 from
+    // key 0, then the window's keys from its first key - an order that depends on the position only
+    const int keep = mask_keep < lo ? mask_keep : lo;
 
     float* qs = smem + warp * dk;
     for (int d = lane; d < dk; d += 32) qs[d] = to_float(q[(size_t)t * q_stride + (size_t)h * q_head_stride + d]);
@@ -90,9 +93,10 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, int q
     const bool vec_ok = dk % VN == 0 && k_row_stride % VN == 0 && k_head_stride % VN == 0 &&
                         (reinterpret_cast<uintptr_t>(kc) % (VN * sizeof(T))) == 0;
 
-    for (int kb = lo; kb <= pos; kb += 32) {
+    for (int kb = keep > 0 ? 0 : lo; kb <= pos; kb = (kb < lo && kb + 32 >= keep) ? lo : kb + 32) {
         const int j = kb + lane;
-        bool valid = j <= pos;
+        const int last = kb < lo ? keep - 1 : pos;     // the last key of the run this block lies in
+        bool valid = j <= last;
         int rowidx = -1;
         if (valid) {
             const int page = bt[j / page_size];
@@ -121,7 +125,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, int q
         l = l * corr + warp_sum(p);
 #pragma unroll
         for (int i = 0; i < MAXD; ++i) acc[i] *= corr;
-        const int cnt = min(32, pos - kb + 1);
+        const int cnt = min(32, last - kb + 1);
         for (int jj = 0; jj < cnt; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const int rj = __shfl_sync(0xffffffffu, rowidx, jj);
@@ -156,8 +160,8 @@ static int launch_generic(const void* q, int q_stride, int q_head_stride, void* 
                           long long k_row_stride, int k_head_stride, const void* vc, long long v_row_stride,
                           int v_head_stride, const int* block_table, int bt_width, const int* positions,
                           const int* tok_seg, int T_, int nh, int nkv, int dk, int dv, int page_size, int num_pages,
-                          int mask_kind, int mask_size, float scale, const void* sink, int sink_bf16, int* err,
-                          cudaStream_t stream) {
+                          int mask_kind, int mask_size, int mask_keep, float scale, const void* sink, int sink_bf16,
+                          int* err, cudaStream_t stream) {
     const int warps = 4;
     const long long total = (long long)T_ * nh;
     const int blocks = (int)((total + warps - 1) / warps);
@@ -167,14 +171,15 @@ static int launch_generic(const void* q, int q_stride, int q_head_stride, void* 
     kern<<<blocks, warps * 32, smem, stream>>>(
         (const T*)q, q_stride, q_head_stride, (T*)out, out_stride, (const T*)kc, k_row_stride, k_head_stride,
         (const T*)vc, v_row_stride, v_head_stride, block_table, bt_width, positions, tok_seg, T_, nh, nkv, dk, dv,
-        page_size, num_pages, mask_kind, mask_size, scale, sink, sink_bf16, err);
+        page_size, num_pages, mask_kind, mask_size, mask_keep, scale, sink, sink_bf16, err);
     return (int)cudaPeekAtLastError();
 }
 
 }  // namespace prism
 
 // Keys of dk and values of dv entries, each plane with its own strides (in elements: between the rows of
-// consecutive cache slots, and between kv heads); mask_kind PRISM_MASK_*; sink: per-head float32 or bf16
+// consecutive cache slots, and between kv heads); mask_kind PRISM_MASK_*; mask_keep: under PRISM_MASK_WINDOW
+// the first mask_keep positions stay visible to every later query; sink: per-head float32 or bf16
 // (sink_dtype) or null.  Returns cudaErrorInvalidValue for dv > 1024 or dk > 12288 / warps.
 PRISM_EXPORT int prism_attention_masked_generic(const void* q, int q_stride, int q_head_stride, void* out,
                                                 int out_stride, const void* kc, long long k_row_stride,
@@ -182,16 +187,17 @@ PRISM_EXPORT int prism_attention_masked_generic(const void* q, int q_stride, int
                                                 int v_head_stride, int dtype, const int* block_table, int bt_width,
                                                 const int* positions, const int* tok_seg, int T, int nh, int nkv,
                                                 int dk, int dv, int page_size, int num_pages, int mask_kind,
-                                                int mask_size, float scale, const void* sink, int sink_dtype,
-                                                int* err, cudaStream_t stream) {
+                                                int mask_size, int mask_keep, float scale, const void* sink,
+                                                int sink_dtype, int* err, cudaStream_t stream) {
     if (T <= 0) return 0;
+    if (mask_keep < 0 || (mask_keep > 0 && mask_kind != PRISM_MASK_WINDOW)) return (int)cudaErrorInvalidValue;
     if (dv > 1024 || dv <= 0 || dk <= 0 || dk > 8192 || nkv <= 0 || nh % nkv != 0) return (int)cudaErrorInvalidValue;
     const int sb = sink_dtype == PRISM_DTYPE_BF16;
 #define PRISM_GENERIC(TT, MD)                                                                                       \
     return prism::launch_generic<TT, MD>(q, q_stride, q_head_stride, out, out_stride, kc, k_row_stride,             \
                                          k_head_stride, vc, v_row_stride, v_head_stride, block_table, bt_width,     \
                                          positions, tok_seg, T, nh, nkv, dk, dv, page_size, num_pages, mask_kind,   \
-                                         mask_size, scale, sink, sb, err, stream)
+                                         mask_size, mask_keep, scale, sink, sb, err, stream)
     if (dtype == PRISM_DTYPE_BF16) {
         if (dv <= 256) PRISM_GENERIC(__nv_bfloat16, 8);
         if (dv <= 512) PRISM_GENERIC(__nv_bfloat16, 16);
@@ -215,6 +221,6 @@ PRISM_EXPORT int prism_attention_generic(const void* q, int q_stride, void* out,
     return prism_attention_masked_generic(q, q_stride, hd, out, out_stride, kc, (long long)nkv * hd, hd, vc,
                                           (long long)nkv * hd, hd, dtype, block_table, bt_width, positions, tok_seg,
                                           T, nh, nkv, hd, hd, page_size, num_pages,
-                                          window > 0 ? PRISM_MASK_WINDOW : PRISM_MASK_CAUSAL, window, scale, nullptr, 0,
+                                          window > 0 ? PRISM_MASK_WINDOW : PRISM_MASK_CAUSAL, window, 0, scale, nullptr, 0,
                                           err, stream);
 }

@@ -56,6 +56,7 @@ struct MaskedAttn {
     const int* seg_start;
     const int* cached_len;
     int nh, nkv, dk, dkp, dv, page_size, num_pages, mask_kind, mask_size;
+    int mask_keep;     // under a window: the first mask_keep positions stay visible to every later query
     float scale_log2;
     const void* sink;
     int sink_bf16;
@@ -84,7 +85,7 @@ __device__ __forceinline__ float ma_exp2(float x) {      // 0 for -inf
 
 // ROWS (32 or 64) cache rows (keys first_key ..) of one kv head into ks[ROWS][kstride] and, unless the values are
 // read out of the key rows, vs[ROWS][vstride].  A row is `kchunks` (`vchunks`) 16-byte pieces, of which the first `kreal`
-// (`vreal`) come from the plane and the rest are zero; keys outside [lo, hi] are zero rows.  Sixteen threads
+// (`vreal`) come from the plane and the rest are zero; keys outside [lo, hi] (and not below `keep`) are zero rows.  Sixteen threads
 // share a row and a thread serves rows tid / 16 + 8 j: it first looks up the slots of its eight rows (eight
 // independent loads of the block table, in flight together), then issues the copies.
 template <bool WITH_V, int ROWS>
@@ -92,7 +93,7 @@ __device__ __forceinline__ void ma_load_tile(__nv_bfloat16* ks, int kstride, int
                                              __nv_bfloat16* vs, int vstride, int vchunks, int vreal,
                                              const __nv_bfloat16* __restrict__ kplane, long long k_row_stride, size_t k_head_off,
                                              const __nv_bfloat16* __restrict__ vplane, long long v_row_stride, size_t v_head_off,
-                                             const int* __restrict__ bt, int first_key, int lo, int hi,
+                                             const int* __restrict__ bt, int first_key, int lo, int hi, int keep,
                                              int page_size, int page_shift, int num_pages, int* err, int tid) {
     const int rr = tid >> 4, cc = tid & 15;
     constexpr int PASSES = ROWS / 8;
@@ -101,7 +102,7 @@ __device__ __forceinline__ void ma_load_tile(__nv_bfloat16* ks, int kstride, int
     for (int j = 0; j < PASSES; ++j) {
         const int key = first_key + rr + 8 * j;
         slot[j] = -1;
-        if (key >= lo && key <= hi) {
+        if ((key >= lo || key < keep) && key <= hi) {
             const int page = page_shift >= 0 ? bt[key >> page_shift] : bt[key / page_size];
             const int in_page = page_shift >= 0 ? (key & (page_size - 1)) : key % page_size;
             if (page < 0 || page >= num_pages) report_error(err, PRISM_ERR_PAGE_RANGE);
@@ -158,12 +159,17 @@ attn_masked_kernel(const MaskedAttn a) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lo = ma_first_key(a.mask_kind, a.mask_size, pos0);
     const int hi = pos0 + ntok - 1;
-    int t0 = lo / MA_TILE, t1 = hi / MA_TILE + 1;
+    // The key tiles this CTA walks: those that hold kept first positions and lie wholly before the window
+    // (tiles 0 .. kt - 1), then the window's (tw0 ..).  v0 .. v1 - 1 counts through both runs.
+    const int tw0 = lo / MA_TILE;
+    const int kt = min((min(a.mask_keep, lo) + MA_TILE - 1) / MA_TILE, tw0);
+    int v0 = 0, v1 = kt + hi / MA_TILE + 1 - tw0;
     if (SPLITK && a.nsplit > 1) {                      // this CTA's share of the key tiles (it may be empty)
-        const int per = (t1 - t0 + a.nsplit - 1) / a.nsplit;
-        t0 += blockIdx.x * per;
-        t1 = min(t1, t0 + per);
+        const int per = (v1 - v0 + a.nsplit - 1) / a.nsplit;
+        v0 += blockIdx.x * per;
+        v1 = min(v1, v0 + per);
     }
+    auto tile_of = [&](int v) { return v < kt ? v : tw0 + (v - kt); };
 
     {   // the CTA's query rows
         const int chunks = a.dkp / 8, real = a.dk / 8;
@@ -180,12 +186,12 @@ attn_masked_kernel(const MaskedAttn a) {
         __nv_bfloat16* ks = KV + (size_t)stage * (k_elems + v_elems);
         ma_load_tile<!V_IN_K, MA_TILE>(ks, kstride, a.dkp / 8, a.dk / 8, ks + k_elems, vstride, DVP / 8, (a.dv + 7) / 8, a.kc,
                               a.k_row_stride, (size_t)kvh * a.k_head_stride, a.vc, a.v_row_stride,
-                              (size_t)kvh * a.v_head_stride, bt, tile * MA_TILE, lo, hi, a.page_size, a.page_shift,
+                              (size_t)kvh * a.v_head_stride, bt, tile * MA_TILE, lo, hi, a.mask_keep, a.page_size, a.page_shift,
                               a.num_pages, a.err, tid);
     };
 #pragma unroll
     for (int st = 0; st < STAGES - 1; ++st) {           // the first group also holds the query rows
-        if (t0 + st < t1) load_tile(t0 + st, st);
+        if (v0 + st < v1) load_tile(tile_of(v0 + st), st);
         cp_async_commit();
     }
 
@@ -214,16 +220,16 @@ attn_masked_kernel(const MaskedAttn a) {
     const int w_lo_last = ma_first_key(a.mask_kind, a.mask_size, w_hi);          // the last row's first key: the largest
     const bool w_all_rows = (rowbase + 15) / a.rpt < ntok && nheads == a.rpt;    // all 16 rows are real
 
-    for (int tile = t0; tile < t1; ++tile) {
-        const int it = tile - t0;
-        if (tile + STAGES - 1 < t1) load_tile(tile + STAGES - 1, (it + STAGES - 1) % STAGES);
+    for (int vt = v0; vt < v1; ++vt) {
+        const int it = vt - v0, tile = tile_of(vt);
+        if (vt + STAGES - 1 < v1) load_tile(tile_of(vt + STAGES - 1), (it + STAGES - 1) % STAGES);
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
         __syncthreads();
         const __nv_bfloat16* Ks = KV + (size_t)(it % STAGES) * (k_elems + v_elems);
         const __nv_bfloat16* Vs = V_IN_K ? Ks : Ks + k_elems;
         const int kfirst = tile * MA_TILE + keybase, klast = kfirst + NT * 8 - 1;
-        if (warp_has_rows && kfirst <= w_hi && klast >= w_lo) {
+        if (warp_has_rows && kfirst <= w_hi && (klast >= w_lo || kfirst < a.mask_keep)) {
             float s[NT][4];
 #pragma unroll
             for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
@@ -248,7 +254,7 @@ attn_masked_kernel(const MaskedAttn a) {
                     for (int e = 0; e < 4; ++e) {
                         const int key = key0 + nt * 8 + (e & 1);
                         const int rr = e >> 1;
-                        const bool vis = ok_row[rr] && key <= p_row[rr] && key >= lo_row[rr];
+                        const bool vis = ok_row[rr] && key <= p_row[rr] && (key >= lo_row[rr] || key < a.mask_keep);
                         const float v = vis ? s[nt][e] * a.scale_log2 : -INFINITY;
                         s[nt][e] = v;
                         mx[rr] = fmaxf(mx[rr], v);
@@ -460,8 +466,8 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
                                              int v_head_stride, const int* block_table, int bt_width,
                                              const int* seg_start, const int* cached_len, int S, int max_q_len,
                                              int nh, int nkv, int dk, int dv, int page_size, int num_pages,
-                                             int mask_kind, int mask_size, float scale, const void* sink,
-                                             int sink_dtype, int few_rows, int nsplit, float* part_o, float* part_ml,
+                                             int mask_kind, int mask_size, int mask_keep, float scale,
+                                             const void* sink, int sink_dtype, int few_rows, int nsplit, float* part_o, float* part_ml,
                                              int* err, cudaStream_t stream) {
     using namespace prism;
     if (S <= 0 || max_q_len <= 0) return 0;
@@ -469,7 +475,7 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
     const bool v_in_k = vc == nullptr;
     if (q_stride % 8 || q_head_stride % 8 || k_row_stride % 8 || k_head_stride % 8 || (uintptr_t)q % 16 || (uintptr_t)kc % 16 ||
         (!v_in_k && (v_row_stride % 8 || v_head_stride % 8 || (uintptr_t)vc % 16 || dv % 8)) || (v_in_k && dv > dk) ||
-        (mask_kind != PRISM_MASK_CAUSAL && mask_size < 1))
+        (mask_kind != PRISM_MASK_CAUSAL && mask_size < 1) || mask_keep < 0 || (mask_keep > 0 && mask_kind != PRISM_MASK_WINDOW))
         return (int)cudaErrorInvalidValue;
     const int rep = nh / nkv;
     if (few_rows && (max_q_len != 1 || nsplit < 1 || nsplit > 65535 ||
@@ -482,7 +488,7 @@ PRISM_EXPORT int prism_attention_masked_bf16(const void* q, long long q_stride, 
     a.vc = (const __nv_bfloat16*)vc; a.v_row_stride = v_row_stride; a.v_head_stride = v_head_stride;
     a.block_table = block_table; a.bt_width = bt_width; a.seg_start = seg_start; a.cached_len = cached_len;
     a.nh = nh; a.nkv = nkv; a.dk = dk; a.dkp = (dk + 15) / 16 * 16; a.dv = dv; a.page_size = page_size;
-    a.num_pages = num_pages; a.mask_kind = mask_kind; a.mask_size = mask_size;
+    a.num_pages = num_pages; a.mask_kind = mask_kind; a.mask_size = mask_size; a.mask_keep = mask_keep;
     a.scale_log2 = scale * 1.4426950408889634f; a.sink = sink; a.sink_bf16 = sink_dtype == PRISM_DTYPE_BF16; a.err = err;
     a.hrows = few_rows ? 16 : MA_ROWS;
     a.rpt = rep < a.hrows ? rep : a.hrows;

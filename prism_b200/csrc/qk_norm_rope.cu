@@ -1,0 +1,94 @@
+// Query/key norm, rotation and cache store for attention layers that norm each head of q and k before they
+// rotate it.  From the float32 result of the input projection, per token:
+//   q_h <- rotate(q_h / sqrt(mean(q_h^2) + eps) * wq)      into q_out [T, nh, dk] (compute dtype)
+//   k_g <- rotate(k_g / sqrt(mean(k_g^2) + eps) * wk)      into the key plane, at the token's slot
+//   v_g                                                    into the value plane, at the token's slot
+// wq, wk: one weight vector of dk entries each, shared by the heads (null: no norm).  The rotation turns the
+// first `rot` entries of a head, entry 2i paired with entry 2i + 1 (interleaved pairs): the pair (a, b) at
+// position p becomes (a cos t - b sin t, b cos t + a sin t), t = p * freq[i]; `freq` is a float32 table
+// of rot / 2 entries (any frequency scaling is in the table), the angle and sincosf are float32.  The slot of
+// position p of request seg is block_table[seg][p / page_size] * page_size + p % page_size.
+// One CTA per token, one warp per head at a time.
+#include "common.cuh"
+
+namespace prism {
+
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(const float* __restrict__ q_in, const float* __restrict__ k_in,
+                                          const float* __restrict__ v_in, long long ps, const void* __restrict__ wq,
+                                          int wq_bf16, const void* __restrict__ wk, int wk_bf16, float eps,
+                                          const float* __restrict__ freq, int rot, T* __restrict__ q_out,
+                                          T* __restrict__ k_plane, T* __restrict__ v_plane,
+                                          const int* __restrict__ block_table, int bt_width,
+                                          const int* __restrict__ positions, const int* __restrict__ tok_seg, int nh, int nkv,
+                                          int dk, int dv, int page_size, int num_pages, int max_pos, int* err) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float* q = pdl_fresh(q_in) + (size_t)t * ps;
+    const float* k = pdl_fresh(k_in) + (size_t)t * ps;
+    const float* v = pdl_fresh(v_in) + (size_t)t * ps;
+    const int pos = positions[t];
+    if (pos < 0 || pos >= max_pos) {
+        if (threadIdx.x == 0) report_error(err, PRISM_ERR_POSITION_RANGE);
+        return;
+    }
+    const int page = block_table[(size_t)tok_seg[t] * bt_width + pos / page_size];
+    const bool page_ok = page >= 0 && page < num_pages;
+    if (!page_ok && threadIdx.x == 0) report_error(err, PRISM_ERR_PAGE_RANGE);
+    const size_t slot = page_ok ? (size_t)page * page_size + pos % page_size : 0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int hh = warp; hh < nh + nkv; hh += nwarps) {
+        const bool is_q = hh < nh;
+        const float* row = is_q ? q + (size_t)hh * dk : k + (size_t)(hh - nh) * dk;
+        const void* w = is_q ? wq : wk;
+        const int wb = is_q ? wq_bf16 : wk_bf16;
+        float inv = 1.f;
+        if (w != nullptr) {
+            float ss = 0.f;
+            for (int d = lane; d < dk; d += 32) ss += row[d] * row[d];
+            ss = warp_sum(ss);
+            inv = 1.f / sqrtf(ss / (float)dk + eps);
+        }
+        if (!is_q && !page_ok) continue;
+        T* dst = is_q ? q_out + ((size_t)t * nh + hh) * dk : k_plane + (slot * nkv + (hh - nh)) * dk;
+        for (int d = lane; d < dk; d += 32) {
+            float a = row[d] * inv * (w != nullptr ? load_param(w, wb, d) : 1.f);
+            if (d < rot) {
+                const int e = d ^ 1;
+                const float b = row[e] * inv * (w != nullptr ? load_param(w, wb, e) : 1.f);
+                float sn, cs;
+                sincosf((float)pos * freq[d >> 1], &sn, &cs);
+                a = (d & 1) ? a * cs + b * sn : a * cs - b * sn;
+            }
+            dst[d] = from_float<T>(a);
+        }
+    }
+    if (page_ok)
+        for (int c = threadIdx.x; c < nkv * dv; c += blockDim.x) v_plane[slot * nkv * dv + c] = from_float<T>(v[c]);
+}
+
+}  // namespace prism
+
+// q, k, v: float32 rows with one row stride `ps` (column blocks of one product); planes [slots, nkv, dk] and
+// [slots, nkv, dv] of `dtype`, q_out [T, nh, dk] of `dtype`; rot even, <= dk.
+PRISM_EXPORT int prism_qk_norm_rope_store(const float* q, const float* k, const float* v, long long ps, const void* wq,
+                                          int wq_dtype, const void* wk, int wk_dtype, float eps, const float* freq, int rot,
+                                          void* q_out, void* k_plane, void* v_plane, int dtype, const int* block_table,
+                                          int bt_width, const int* positions, const int* tok_seg, int T, int nh, int nkv, int dk,
+                                          int dv, int page_size, int num_pages, int max_pos, int* err, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rot < 0 || rot > dk || rot % 2 || (rot > 0 && freq == nullptr) || nh < 1 || nkv < 1 || dk < 1 || dv < 1)
+        return (int)cudaErrorInvalidValue;
+    const int heads = nh + nkv;
+    const int threads = heads >= 8 ? 256 : (heads >= 4 ? 128 : 64);
+    const int qb = wq_dtype == PRISM_DTYPE_BF16, kb = wk_dtype == PRISM_DTYPE_BF16;
+    if (dtype == PRISM_DTYPE_BF16)
+        return (int)prism::launch_kernel(prism::qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, q, k,
+                                         v, ps, wq, qb, wk, kb, eps, freq, rot, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_plane,
+                                         (__nv_bfloat16*)v_plane, block_table, bt_width, positions, tok_seg, nh, nkv, dk, dv,
+                                         page_size, num_pages, max_pos, err);
+    return (int)prism::launch_kernel(prism::qk_norm_rope_store_kernel<float>, dim3(T), dim3(threads), 0, stream, q, k, v, ps, wq,
+                                     qb, wk, kb, eps, freq, rot, (float*)q_out, (float*)k_plane, (float*)v_plane, block_table,
+                                     bt_width, positions, tok_seg, nh, nkv, dk, dv, page_size, num_pages, max_pos, err);
+}

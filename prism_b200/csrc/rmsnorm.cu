@@ -100,7 +100,58 @@ __global__ void __launch_bounds__(1024) add_rmsnorm_vec_kernel(float* __restrict
     }
 }
 
+// Norm after the sum, for layers whose residual stream is itself normed:
+//   x[r, :] <- (alpha x[r, :] + sum_s delta[s, r, :]) * rsqrt(mean((..)^2) + eps) * w        (float32, in place)
+//   copy[r, :] = x[r, :] in the compute dtype (optional: what the next sublayer's matrix products read)
+// One block per row; a thread touches only its own columns, so the row can be rewritten in place.
+template <typename TD, typename TO>
+__global__ void scale_add_rmsnorm_kernel(float* __restrict__ x, float alpha, const TD* __restrict__ delta_in, int nsplit,
+                                         size_t split_stride, const void* __restrict__ weight, int weight_bf16, float eps,
+                                         TO* __restrict__ copy, int H) {
+    pdl_trigger();
+    pdl_wait();
+    const TD* delta = pdl_fresh(delta_in);
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    float* row = x + (size_t)r * H;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = alpha * row[c];
+        if (delta != nullptr)
+            for (int s = 0; s < nsplit; ++s) v += to_float(delta[(size_t)s * split_stride + (size_t)r * H + c]);
+        row[c] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = row[c] * inv * load_param(weight, weight_bf16, c);
+        row[c] = v;
+        if (copy != nullptr) copy[(size_t)r * H + c] = from_float<TO>(v);
+    }
+}
+
 }  // namespace prism
+
+// x float32 [rows, H] in place; delta (null: none) [nsplit, rows, H] of delta_dtype; copy (null: none) [rows, H] of
+// copy_dtype.
+PRISM_EXPORT int prism_scale_add_rmsnorm(float* x, float alpha, const void* delta, int delta_dtype, int nsplit,
+                                         long long split_stride, const void* weight, int weight_dtype, float eps,
+                                         void* copy, int copy_dtype, int rows, int H, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int wb = weight_dtype == PRISM_DTYPE_BF16;
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+#define LAUNCH(TD, TO)                                                                                              \
+    return (int)prism::launch_kernel(prism::scale_add_rmsnorm_kernel<TD, TO>, dim3(rows), dim3(threads), 0, stream, x,  \
+                                     alpha, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, (TO*)copy, H)
+    if (delta_dtype == PRISM_DTYPE_BF16) {
+        if (copy_dtype == PRISM_DTYPE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+        LAUNCH(__nv_bfloat16, float);
+    }
+    if (copy_dtype == PRISM_DTYPE_BF16) LAUNCH(float, __nv_bfloat16);
+    LAUNCH(float, float);
+#undef LAUNCH
+}
 
 // delta_dtype / out_dtype: PRISM_DTYPE_*.  delta may be null (plain norm).
 PRISM_EXPORT int prism_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int nsplit,

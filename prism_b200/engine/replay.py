@@ -52,7 +52,7 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=64, help="tokens per cache page")
-    ap.add_argument("--max-live", type=int, default=8, help="request slots")
+    ap.add_argument("--max-live", type=int, default=4, help="request slots (state slots of recurrent layers included)")
     ap.add_argument("--gpu", type=int, default=0)
     args = ap.parse_args(argv)
 

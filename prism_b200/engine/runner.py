@@ -66,7 +66,7 @@ class ModelRunner:
         # the whole model out of graphs: such steps run eagerly, with the same results
         from ..parts.base import Mixer
         self.graph_safe = all(
-            (m.graph_safe if m.graph_safe is not None else m.cache_need().kind != "state")
+            (m.graph_safe if m.graph_safe is not None else all(n.kind != "state" for n in m.cache_needs()))
             for m in model.walk() if isinstance(m, Mixer))
         self.use_cuda_graph = bool(use_cuda_graph) and self.graph_safe
         self.graph_batch_sizes = sorted(set(int(b) for b in graph_batch_sizes if b <= max_seqs)) or [1]

@@ -30,15 +30,18 @@ from .models.decoder import DecoderModel, ModelSpec
 @dataclass
 class Architecture:
     name: str
-    parse_config: Callable[[dict], object]       # raw config.json dict -> typed config
+    parse_config: Callable[..., object]          # raw config.json dict -> typed config
     build_spec: Callable[[object], ModelSpec]    # typed config -> layer plan
+    # True: a size of this design is given by a tensor's shape only; ``parse_config(raw, shapes)`` then gets
+    # ``{tensor name: shape}`` of the model file as well (None where there is no file: random weights)
+    sizes_from_tensors: bool = False
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config, build_spec) -> None:
-    _ARCHITECTURES[name] = Architecture(name, parse_config, build_spec)
+def register_architecture(name: str, parse_config, build_spec, sizes_from_tensors: bool = False) -> None:
+    _ARCHITECTURES[name] = Architecture(name, parse_config, build_spec, sizes_from_tensors)
 
 
 _builtin_loaded = False
@@ -76,8 +79,9 @@ def resolve(raw_config: dict) -> Architecture:
     return _ARCHITECTURES[name]
 
 
-def build_model(raw_config: dict):
-    """``(typed config, DecoderModel)`` for a raw config.json dict."""
+def build_model(raw_config: dict, tensor_shapes: dict = None):
+    """``(typed config, DecoderModel)`` for a raw config.json dict; ``tensor_shapes``: the model file's ``{tensor
+    name: shape}`` where there is one, for designs that take a size from it."""
     arch = resolve(raw_config)
-    cfg = arch.parse_config(raw_config)
+    cfg = arch.parse_config(raw_config, tensor_shapes) if arch.sizes_from_tensors else arch.parse_config(raw_config)
     return cfg, DecoderModel(arch.build_spec(cfg))

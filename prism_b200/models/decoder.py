@@ -58,13 +58,25 @@ class DecoderModel(Part):
                 src = ent.reads_cache_of
                 if not 0 <= src < e or self.schedule[src].reads_cache_of is not None:
                     raise ValueError(f"schedule entry {e} must read the cache of an earlier entry that owns one")
+                if len(self.layers[ent.layer].cache_needs()) > 1 or len(self.layers[self.schedule[src].layer].cache_needs()) > 1:
+                    raise ValueError(f"schedule entry {e}: a layer that keeps several things between steps can "
+                                     f"neither lend its cache nor read another's")
                 if self.layers[ent.layer].cache_need().group_key() != self.layers[self.schedule[src].layer].cache_need().group_key():
                     raise ValueError(f"schedule entry {e} reads a cache of a different shape")
 
-    def cache_needs(self) -> List[Optional[CacheNeed]]:
-        """Per schedule entry: the cache plane it owns (None if it reads another's)."""
-        return [None if ent.reads_cache_of is not None else self.layers[ent.layer].cache_need()
-                for ent in self.schedule]
+    def cache_needs(self) -> list:
+        """Per schedule entry: the cache plane it owns (None if it reads another's); a tuple of them for a
+        layer whose mixer keeps several things between steps (``Mixer.cache_needs``)."""
+        out = []
+        for ent in self.schedule:
+            needs = self.layers[ent.layer].cache_needs()
+            if ent.reads_cache_of is not None:
+                out.append(None)
+            elif len(needs) > 1:
+                out.append(tuple(needs))
+            else:
+                out.append(needs[0] if needs else self.layers[ent.layer].cache_need())
+        return out
 
     def forward(self, ctx, cache_views):
         """Run the step's tokens; returns float32 logits ``[R, V]`` for

@@ -91,10 +91,19 @@ class _Sig:
     prism_attention_generic = [_p, _i, _p, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
                                _i, _f, _p, _p]
     prism_attention_masked_generic = [_p, _i, _i, _p, _i, _p, _ll, _i, _p, _ll, _i, _i, _p, _i, _p, _p, _i, _i, _i,
-                                      _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _p]
+                                      _i, _i, _i, _i, _i, _i, _i, _f, _p, _i, _p, _p]
     prism_attention_masked_supported = [_i, _i, _i, _i]
     prism_attention_masked_bf16 = [_p, _ll, _i, _p, _ll, _p, _ll, _i, _p, _ll, _i, _p, _i, _p, _p, _i, _i, _i, _i, _i, _i,
-                                   _i, _i, _i, _i, _f, _p, _i, _i, _i, _p, _p, _p, _p]
+                                   _i, _i, _i, _i, _i, _f, _p, _i, _i, _i, _p, _p, _p, _p]
+    prism_scale_add_rmsnorm = [_p, _f, _p, _i, _i, _ll, _p, _i, _f, _p, _i, _i, _i, _p]
+    prism_gated_product = [_p, _ll, _p, _ll, _p, _ll, _i, _i, _i, _i, _f, _p]
+    prism_qk_norm_rope_store = [_p, _p, _p, _ll, _p, _i, _p, _i, _f, _p, _i, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i,
+                                _i, _i, _i, _i, _p, _p]
+    prism_conv_unit_gates = [_p, _ll, _i, _i, _p, _i, _i, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _p]
+    prism_state_tail = [_p, _ll, _i, _p, _i, _p, _p, _i, _p]
+    prism_shift_mix = [_p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _ll, _p]
+    prism_headnorm_gate = [_p, _p, _ll, _p, _i, _i, _f, _f, _i, _i, _i, _p, _i, _ll, _p]
+    prism_recurrent_scan = [_i, _p, _ll, _i, _i, _i, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _i,
                              _p, _ll, _p]
@@ -1134,24 +1143,27 @@ class KeyMask:
     """Which keys a position sees; every kind is causal.  ``causal``: all keys
     from 0; ``window(n)``: the last n (itself and the n - 1 before it);
     ``chunk(n)``: those of its own block of n positions, blocks counted from
-    position 0 of the sequence."""
+    position 0 of the sequence.  ``window(n, keep_first=m)``: the last n and,
+    however far back, the first m positions of the sequence."""
 
-    __slots__ = ("kind", "size")
+    __slots__ = ("kind", "size", "keep")
 
-    def __init__(self, kind: int = MASK_CAUSAL, size: int = 0):
+    def __init__(self, kind: int = MASK_CAUSAL, size: int = 0, keep: int = 0):
         if kind not in (MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK):
             raise ValueError(f"unknown mask kind {kind}")
         if kind != MASK_CAUSAL and int(size) < 1:
             raise ValueError(f"a window or chunk needs a size of at least 1, got {size}")
-        self.kind, self.size = int(kind), int(size) if kind != MASK_CAUSAL else 0
+        if int(keep) < 0 or (keep and kind != MASK_WINDOW):
+            raise ValueError("only a window keeps first positions visible, and not a negative number of them")
+        self.kind, self.size, self.keep = int(kind), int(size) if kind != MASK_CAUSAL else 0, int(keep)
 
     @classmethod
     def causal(cls):
         return cls()
 
     @classmethod
-    def window(cls, n: Optional[int]):
-        return cls() if not n else cls(MASK_WINDOW, n)
+    def window(cls, n: Optional[int], keep_first: int = 0):
+        return cls() if not n else cls(MASK_WINDOW, n, keep_first)
 
     @classmethod
     def chunk(cls, n: Optional[int]):
@@ -1165,11 +1177,14 @@ class KeyMask:
             return pos // self.size * self.size
         return 0
 
+    def sees(self, pos: int, key: int) -> bool:
+        return key <= pos and (key >= self.first_key(pos) or key < self.keep)
+
     def most_keys(self, max_kv_len: int) -> int:
-        return max_kv_len if self.kind == MASK_CAUSAL else min(max_kv_len, self.size)
+        return max_kv_len if self.kind == MASK_CAUSAL else min(max_kv_len, self.size + self.keep)
 
     def __repr__(self):
-        return f"KeyMask({('causal', 'window', 'chunk')[self.kind]}, {self.size})"
+        return f"KeyMask({('causal', 'window', 'chunk')[self.kind]}, {self.size}" + (f", keep_first={self.keep})" if self.keep else ")")
 
 
 def _plane_strides(plane: torch.Tensor):
@@ -1202,8 +1217,8 @@ def attention_masked_generic(q: torch.Tensor, out: torch.Tensor, k_plane: torch.
         _ptr(q), q.stride(0) if T > 1 else nh * dk, q.stride(1) if nh > 1 else dk, _ptr(out),
         out.stride(0) if T > 1 else nh * dv, _ptr(k_plane), krs, khs, _ptr(v_plane), vrs, vhs, _dt(q),
         _ptr(block_table), block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, nh, nkv, dk, dv, P, num_pages,
-        mask.kind, mask.size, float(scale), _ptr(sink), F32 if sink is None else _dt(sink), _ptr(err), _stream()),
-        "attention_masked_generic")
+        mask.kind, mask.size, mask.keep, float(scale), _ptr(sink), F32 if sink is None else _dt(sink), _ptr(err),
+        _stream()), "attention_masked_generic")
 
 
 def cache_store(src: torch.Tensor, plane: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
@@ -1271,7 +1286,7 @@ def rotate_slice(src: torch.Tensor, dst: torch.Tensor, rot_dims: int, inv_freq: 
            "rotate_slice")
 
 
-ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}      # csrc/activation.cu: PRISM_ACT_*
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3, "tanh": 4, "sigmoid": 5}      # csrc/activation.cu: PRISM_ACT_*
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str):
@@ -1361,7 +1376,7 @@ def attention_masked_bf16(q, out, k_plane, v_plane, block_table, seg_start, cach
         _ptr(q), q.stride(0) if T > 1 else nh * dk, q.stride(1) if nh > 1 else dk, _ptr(out),
         out.stride(0) if T > 1 else nh * dv, _ptr(k_plane), krs, khs, None if vin else _ptr(v_plane), vrs, vhs,
         _ptr(block_table), block_table.shape[1], _ptr(seg_start), _ptr(cached_len), S, int(max_q_len), nh, nkv, dk, dv,
-        P, num_pages, mask.kind, mask.size, float(scale), _ptr(sink), F32 if sink is None else _dt(sink),
+        P, num_pages, mask.kind, mask.size, mask.keep, float(scale), _ptr(sink), F32 if sink is None else _dt(sink),
         1 if few_rows else 0, int(nsplit) if few_rows else 1, _ptr(po), _ptr(pml), _ptr(err), _stream()),
         "attention_masked_bf16")
     if few_rows and nsplit > 1:
@@ -1423,3 +1438,152 @@ def matmul_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor):
             sgemm(x[:, h], w[h], None, out[:, h])
         return
     torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+
+
+# --------------------------------------------------------------------------
+# norm after the sum, query/key norm with interleaved rotation, gates, recurrent mixers
+# --------------------------------------------------------------------------
+
+def scale_add_rmsnorm(x: torch.Tensor, alpha: float, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                      copy: Optional[torch.Tensor] = None):
+    """``x <- rmsnorm(alpha * x + delta) * weight`` in place on the float32 rows ``x [T, H]``; ``delta``: None,
+    ``[T, H]`` or a stack ``[k, T, H]`` of partial sums (any dtype of the kernels).  ``copy [T, H]``: receives the
+    new rows in its own dtype (what a bf16 matrix product reads next)."""
+    _cuda(x, delta, weight, copy)
+    assert x.dtype == torch.float32 and x.is_contiguous() and weight.shape == (x.shape[1],) and weight.is_contiguous()
+    T, H = x.shape
+    nsplit = 0
+    if delta is not None:
+        assert delta.is_contiguous() and delta.shape[-2:] == (T, H)
+        nsplit = 1 if delta.dim() == 2 else delta.shape[0]
+    if copy is not None:
+        assert copy.shape == (T, H) and copy.is_contiguous()
+    _check(lib().prism_scale_add_rmsnorm(_ptr(x), float(alpha), _ptr(delta), F32 if delta is None else _dt(delta), nsplit,
+                                         T * H, _ptr(weight), _dt(weight), float(eps), _ptr(copy),
+                                         F32 if copy is None else _dt(copy), T, H, _stream()), "scale_add_rmsnorm")
+
+
+def gated_product(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, kind: str = "sigmoid", scale: float = 1.0):
+    """``out = x * act(gate) * scale``; ``x`` and ``out`` ``[rows, cols]`` in the compute dtype, ``gate`` float32,
+    each with a row stride of its own; ``kind``: ``sigmoid`` or ``silu``."""
+    _cuda(x, gate, out)
+    rows, cols = x.shape
+    assert gate.dtype == torch.float32 and gate.shape == x.shape and out.shape == x.shape and out.dtype == x.dtype
+    assert x.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
+    _check(lib().prism_gated_product(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), _dt(x),
+                                     rows, cols, ACTIVATIONS[kind], float(scale), _stream()), "gated_product")
+
+
+def qk_norm_rope_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weight: Optional[torch.Tensor],
+                       k_weight: Optional[torch.Tensor], eps: float, freq: Optional[torch.Tensor], rot: int,
+                       q_out: torch.Tensor, k_plane: torch.Tensor, v_plane: torch.Tensor, block_table: torch.Tensor,
+                       positions: torch.Tensor, tok_seg: torch.Tensor, num_pages: int, max_pos: int, err: torch.Tensor):
+    """From float32 column blocks ``q [T, nh * dk]``, ``k [T, nkv * dk]``, ``v [T, nkv * dv]`` of one product (one
+    row stride): RMS norm of every q and k head with ``q_weight`` / ``k_weight`` (``[dk]``, None: no norm), rotation
+    of the first ``rot`` entries in interleaved pairs by ``position * freq[i]``; q into ``q_out [T, nh, dk]``, k and v
+    into their cache planes at the token's slot."""
+    _cuda(q, k, v, q_weight, k_weight, freq, q_out, k_plane, v_plane, block_table, positions, tok_seg)
+    T, nh, dk = q_out.shape
+    nkv, dv = k_plane.shape[2], v_plane.shape[3]
+    assert q.dtype == k.dtype == v.dtype == torch.float32 and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert q.shape == (T, nh * dk) and k.shape == (T, nkv * dk) and v.shape == (T, nkv * dv)
+    assert T == 1 or q.stride(0) == k.stride(0) == v.stride(0)
+    assert q_out.is_contiguous() and k_plane.is_contiguous() and v_plane.is_contiguous()
+    assert k_plane.dtype == q_out.dtype == v_plane.dtype and k_plane.shape[3] == dk and k_plane.shape[:3] == v_plane.shape[:3]
+    if rot:
+        assert freq.dtype == torch.float32 and freq.shape == (rot // 2,) and freq.is_contiguous()
+    for w in (q_weight, k_weight):
+        assert w is None or (w.shape == (dk,) and w.is_contiguous())
+    _check(lib().prism_qk_norm_rope_store(
+        _ptr(q), _ptr(k), _ptr(v), q.stride(0), _ptr(q_weight), F32 if q_weight is None else _dt(q_weight), _ptr(k_weight),
+        F32 if k_weight is None else _dt(k_weight), float(eps), _ptr(freq), int(rot), _ptr(q_out), _ptr(k_plane),
+        _ptr(v_plane), _dt(q_out), _ptr(block_table), block_table.shape[1], _ptr(positions), _ptr(tok_seg), T, nh, nkv, dk,
+        dv, k_plane.shape[1], num_pages, int(max_pos), _ptr(err), _stream()), "qk_norm_rope_store")
+
+
+def conv_unit_gates(proj: torch.Tensor, b_off: int, a_off: int, taps: torch.Tensor, tail: torch.Tensor,
+                    a_log: torch.Tensor, dt_bias: torch.Tensor, ctx, G: int, H: int, dk: int, dv: int, unit_eps: float,
+                    qkv: torch.Tensor, bg: torch.Tensor):
+    """The input side of the gated delta rule from the float32 projection rows ``proj`` (columns ``[0, C)``: the q
+    | k | v channels, ``C = 2 G dk + H dv``; ``b_off``/``a_off``: first column of the beta / decay projections):
+    short causal convolution over time with ``taps [C, K]`` (the ``K - 1`` inputs before the step in ``tail
+    [slots, K - 1, C]``) and silu; q and k heads made unit vectors (q also times ``dk^-1/2``) into ``qkv [T, C]``;
+    ``bg [T, 2 H]`` = sigmoid(b) | exp(-exp(a_log) softplus(a + dt_bias))."""
+    _cuda(proj, taps, tail, a_log, dt_bias, qkv, bg)
+    T = proj.shape[0]
+    C, K = taps.shape
+    assert C == 2 * G * dk + H * dv and proj.dtype == torch.float32 and proj.stride(1) == 1 and taps.is_contiguous()
+    assert tail.dtype == torch.float32 and tail.is_contiguous() and tuple(tail.shape[1:]) == (max(K - 1, 0), C)
+    assert qkv.shape == (T, C) and qkv.is_contiguous() and bg.shape == (T, 2 * H) and bg.is_contiguous()
+    assert qkv.dtype == torch.float32 and bg.dtype == torch.float32 and a_log.shape == (H,) and dt_bias.shape == (H,)
+    _check(lib().prism_conv_unit_gates(_ptr(proj), proj.stride(0), int(b_off), int(a_off), _ptr(taps), _dt(taps), K,
+                                       _ptr(tail), _ptr(a_log), _dt(a_log), _ptr(dt_bias), _dt(dt_bias), _ptr(ctx.tok_seg),
+                                       _ptr(ctx.seg_start), _ptr(ctx.state_slots), T, G, H, dk, dv, float(unit_eps),
+                                       _ptr(qkv), _ptr(bg), _stream()), "conv_unit_gates")
+
+
+def state_tail(src: torch.Tensor, tail: torch.Tensor, ctx):
+    """Per request of the step: the last ``rows`` rows of its input so far (``src [T, width]`` float32, row stride
+    free, holds this step's) into ``tail [slots, rows, width]``; rows the step does not reach back to move up from
+    the tail as it was."""
+    _cuda(src, tail)
+    rows, width = tail.shape[1], tail.shape[2]
+    if rows == 0:
+        return
+    assert src.dtype == torch.float32 and tail.dtype == torch.float32 and tail.is_contiguous() and src.stride(1) == 1
+    assert src.shape[1] >= width
+    _check(lib().prism_state_tail(_ptr(src), src.stride(0), width, _ptr(tail), rows, _ptr(ctx.seg_start),
+                                  _ptr(ctx.state_slots), ctx.S, _stream()), "state_tail")
+
+
+def shift_mix(x: torch.Tensor, prev: torch.Tensor, mu: torch.Tensor, ctx, out: torch.Tensor):
+    """``out[s] = x + (x_prev - x) * mu[s]`` for ``mu [n, D]``; ``x [T, D]`` float32, ``x_prev`` the row before in
+    the same request (``prev [slots, 1, D]`` for a step's first token); ``out [n, T, D]`` in the compute dtype."""
+    _cuda(x, prev, mu, out)
+    T, D = x.shape
+    n = mu.shape[0]
+    assert x.dtype == torch.float32 and x.is_contiguous() and prev.dtype == torch.float32 and prev.is_contiguous()
+    assert prev[0].numel() == D and mu.shape == (n, D) and mu.is_contiguous() and out.shape == (n, T, D) and out.is_contiguous()
+    _check(lib().prism_shift_mix(_ptr(x), D, _ptr(prev), _ptr(mu), _dt(mu), n, _ptr(ctx.tok_seg), _ptr(ctx.seg_start),
+                                 _ptr(ctx.state_slots), T, _ptr(out), _dt(out), T * D, _stream()), "shift_mix")
+
+
+def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, scale: float, out: torch.Tensor):
+    """``out[t, h] = o[t, h] / rms(o[t, h]) * weight * silu(gate[t, h]) * scale``; ``o [T, H, dv]`` float32, ``gate
+    [T, H * dv]`` float32 and ``out [T, H * dv]`` (compute dtype) with row strides of their own; ``weight [dv]`` (one
+    for all heads) or ``[H * dv]``."""
+    _cuda(o, gate, weight, out)
+    T, H, dv = o.shape
+    assert o.dtype == torch.float32 and o.is_contiguous() and gate.dtype == torch.float32 and gate.stride(1) == 1
+    assert gate.shape == (T, H * dv) and out.shape == (T, H * dv) and out.stride(1) == 1 and weight.is_contiguous()
+    assert weight.shape in ((dv,), (H * dv,))
+    per_head = 1 if (weight.shape[0] == H * dv and H > 1) else 0
+    _check(lib().prism_headnorm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _dt(weight), per_head, float(eps),
+                                     float(scale), T, H, dv, _ptr(out), _dt(out), out.stride(0), _stream()), "headnorm_gate")
+
+
+SCAN_DELTA, SCAN_BONUS = 0, 1      # csrc/recurrent.cu: PRISM_SCAN_*
+
+
+def recurrent_scan(mode: int, x: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, ctx, H: int,
+                   rep: int, dk: int, dv: int, out: torch.Tensor, bg: Optional[torch.Tensor] = None,
+                   ww: Optional[torch.Tensor] = None, w0: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None):
+    """The step's tokens through a matrix-state recurrence, request by request, token after token, from and
+    into ``state [slots, H, dv, dk]`` (float32).  ``x``: float32 rows holding q (or r) at column ``q_off``, k at
+    ``k_off``, v at ``v_off``.  ``SCAN_DELTA``: delta rule with ``bg [T, 2 H]`` (beta | scalar decay), ``rep`` heads
+    share a q/k head.  ``SCAN_BONUS``: per-channel decay ``exp(-exp(ww + w0))`` (``ww [T, H * dk]``) and bonus ``u [H
+    * dk]`` for the current token.  ``out [T, H, dv]`` float32."""
+    _cuda(x, state, out, bg, ww, w0, u)
+    T = x.shape[0]
+    assert x.dtype == torch.float32 and x.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
+    assert tuple(state.shape[1:]) == (H, dv, dk) and out.shape == (T, H, dv) and out.is_contiguous() and out.dtype == torch.float32
+    if mode == SCAN_DELTA:
+        assert bg is not None and bg.shape == (T, 2 * H) and bg.is_contiguous() and bg.dtype == torch.float32
+    else:
+        assert ww.dtype == torch.float32 and ww.shape == (T, H * dk) and ww.stride(1) == 1
+        assert w0.numel() == H * dk and u.numel() == H * dk and w0.is_contiguous() and u.is_contiguous()
+    _check(lib().prism_recurrent_scan(
+        int(mode), _ptr(x), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(bg), _ptr(ww),
+        0 if ww is None else ww.stride(0), _ptr(w0), F32 if w0 is None else _dt(w0), _ptr(u), F32 if u is None else _dt(u),
+        _ptr(state), _ptr(ctx.seg_start), _ptr(ctx.state_slots), ctx.S, H, rep, dk, dv, _ptr(out), _stream()),
+        "recurrent_scan")

@@ -33,17 +33,26 @@ class GQAAttention(Mixer):
     softmax's denominator, unscaled and without a value.  ``own_kv`` False: no key and value projections;
     the layer's run must read another run's cache plane (``ScheduleEntry.reads_cache_of``).
     ``cache_chunk``: the block size by which the cache gives pages back - ``"mask"``: that of this layer's
-    mask; None: never (a plane that layers with different masks read).  ``names``: the tensors' names in
-    the model file (keys q, k, v, o, q_b, k_b, v_b, o_b, sink)."""
+    mask; None: never (a plane that layers with different masks read).  ``keep_first``: under a window, the
+    first ``keep_first`` positions of the sequence stay visible to every later query (at their true positions).
+    ``qk_norm_eps``: every head of q and k is RMS-normed over ``head_dim`` before it is rotated, with one weight
+    vector for q and one for k that all heads share.  ``gate``: the concatenated heads are multiplied by
+    ``sigmoid(W_g h)`` before the output projection.  ``out_scale``: a constant on the layer's result (folded into
+    the gate).  A rotation in interleaved pairs (``RotaryParams.interleaved``), the query/key norm and the gate
+    work from the float32 result of the input projection.  ``names``: the tensors' names in the model file (keys
+    q, k, v, o, q_b, k_b, v_b, o_b, sink, q_norm, k_norm, g)."""
 
     NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight",
-                 q_b="q_proj.bias", k_b="k_proj.bias", v_b="v_proj.bias", o_b="o_proj.bias", sink="sinks")
+                 q_b="q_proj.bias", k_b="k_proj.bias", v_b="v_proj.bias", o_b="o_proj.bias", sink="sinks",
+                 q_norm="q_norm.weight", k_norm="k_norm.weight", g="g_proj.weight")
+    graph_safe = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qkv_bias: bool = True, o_bias: bool = False, window: Optional[int] = None,
                  position: Optional[PartSpec] = None, scale: Optional[float] = None,
                  v_head_dim: Optional[int] = None, chunk: Optional[int] = None, sink: bool = False,
-                 own_kv: bool = True, cache_chunk="mask", names: Optional[dict] = None):
+                 own_kv: bool = True, cache_chunk="mask", names: Optional[dict] = None, keep_first: int = 0,
+                 qk_norm_eps: Optional[float] = None, gate: bool = False, out_scale: float = 1.0):
         if num_heads % num_kv_heads:
             raise ConfigError(f"num_heads {num_heads} not divisible by num_kv_heads {num_kv_heads}")
         self.hidden_size, self.nh, self.nkv, self.hd = int(hidden_size), int(num_heads), int(num_kv_heads), int(head_dim)
@@ -62,7 +71,19 @@ class GQAAttention(Mixer):
         self.names = dict(self.NAMES, **(names or {}))
         # what the fused rotate-and-store and the equal-size attention kernels do not cover goes the general way:
         # projection, (rotation,) one store per plane, attention under a KeyMask
-        self.general = self.vhd != self.hd or self.chunk is not None or self.sink or not self.own_kv
+        self.keep_first = int(keep_first)
+        if self.keep_first < 0 or (self.keep_first and self.window is None):
+            raise ConfigError("keep_first: a number of first positions, kept visible behind a window")
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.gate, self.out_scale = bool(gate), float(out_scale)
+        interleaved = bool(position and position.kind == "rotary_scaled" and position.args.get("interleaved", True))
+        # query/key norm, interleaved pairs and the gate read the input projection's float32 result
+        self.float32_projection = self.qk_norm_eps is not None or self.gate or interleaved
+        if self.float32_projection and (not self.own_kv or qkv_bias):
+            raise ConfigError("query/key norm, interleaved rotation and output gate: for layers with key and value "
+                              "projections of their own and without biases on them")
+        self.general = (self.vhd != self.hd or self.chunk is not None or self.sink or not self.own_kv
+                        or self.keep_first > 0 or self.float32_projection)
         self._own_in = self._own_out = True
         # the equal-size kernels keep a head's row in a warp's registers and rotate pairs; the general path takes
         # any key size (its kernels loop over it) and values of up to 1024 entries
@@ -72,7 +93,8 @@ class GQAAttention(Mixer):
         if self.general and (self.hd < 1 or self.vhd > 1024):
             raise ConfigError(f"head_dim {head_dim}, value size {self.vhd}: keys need at least one entry and values "
                               f"at most 1024")
-        self.mask = ops.KeyMask.chunk(self.chunk) if self.chunk is not None else ops.KeyMask.window(self.window)
+        self.mask = (ops.KeyMask.chunk(self.chunk) if self.chunk is not None
+                     else ops.KeyMask.window(self.window, self.keep_first))
 
     @property
     def q_size(self):
@@ -88,7 +110,8 @@ class GQAAttention(Mixer):
 
     def cache_need(self):
         return CacheNeed("paged", self.nkv, self.hd, self.window,
-                         v_head_dim=None if self.vhd == self.hd else self.vhd, chunk=self.cache_chunk)
+                         v_head_dim=None if self.vhd == self.hd else self.vhd, chunk=self.cache_chunk,
+                         keep_first=self.keep_first)
 
     def _in_sources(self):
         H, qs, kvs, vs, n = self.hidden_size, self.q_size, self.kv_size, self.v_size, self.names
@@ -97,6 +120,8 @@ class GQAAttention(Mixer):
         if self.own_kv:
             w += [WeightSource(n["k"], (kvs, H)), WeightSource(n["v"], (vs, H))]
             b += [WeightSource(n["k_b"], (kvs,), "bias"), WeightSource(n["v_b"], (vs,), "bias")]
+        if self.gate:
+            w.append(WeightSource(n["g"], (self.nh * self.vhd, H)))
         return tuple(w), tuple(b) if self.qkv_bias else ()
 
     def _out_sources(self):
@@ -113,6 +138,9 @@ class GQAAttention(Mixer):
                 ps.append(ParamSpec("qkv_b", b))
         if self.sink:
             ps.append(ParamSpec("sink", (WeightSource(self.names["sink"], (self.nh,), "bias"),)))
+        if self.qk_norm_eps is not None:
+            ps.append(ParamSpec("q_norm", (WeightSource(self.names["q_norm"], (self.hd,), "norm"),)))
+            ps.append(ParamSpec("k_norm", (WeightSource(self.names["k_norm"], (self.hd,), "norm"),)))
         if self._own_out:
             w, b = self._out_sources()
             ps.append(ParamSpec("o_w", w))
@@ -141,7 +169,8 @@ class GQAAttention(Mixer):
             return None
         self._own_in = False
         w, b = self._in_sources()
-        return DetachedProjection(self.handed_over(*w), self.handed_over(*b), sum(s.shape[0] for s in w))
+        return DetachedProjection(self.handed_over(*w), self.handed_over(*b), sum(s.shape[0] for s in w),
+                                  float32=self.float32_projection)
 
     def on_bound(self):
         # Said once, when the model is built, not found out from the step time: in bfloat16 the tensor-core
@@ -165,6 +194,8 @@ class GQAAttention(Mixer):
         if cache.write != self.own_kv:
             raise ValueError("a layer without key and value projections must read another run's cache plane, "
                              "and one with them owns its plane")
+        if self.float32_projection:
+            return self._forward_inner_f32(ctx, x, cache, out, proj)
         qkv = proj if proj is not None else ops.linear(x, self.w["qkv_w"], self.w.get("qkv_b"))
         q = qkv[:, :qs].view(T, self.nh, self.hd)
         k = qkv[:, qs:qs + kvs].view(T, self.nkv, self.hd) if self.own_kv else None
@@ -182,9 +213,31 @@ class GQAAttention(Mixer):
         ops.masked_attention(ctx, q, out, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
                              self.w.get("sink"))
 
+    def _forward_inner_f32(self, ctx, x, cache, out, proj):
+        """From the float32 projection ``[q | k | v | gate]``: one launch norms and rotates q and k and stores k
+        and v at the tokens' slots; attention under the mask; the gate (and ``out_scale``) on its way into ``out``."""
+        T, qs, kvs, vs = x.shape[0], self.q_size, self.kv_size, self.v_size
+        if proj is None:
+            proj = ops.linear(x, self.w["qkv_w"], None, out_dtype=torch.float32)
+        rot = self.position.rotary() if self.position is not None else None
+        if self.position is not None and (rot is None or (rot.rotary_dim and not rot.interleaved)):
+            raise ConfigError("with query/key norm or an output gate the attention part rotates interleaved pairs only")
+        q = ctx.alloc((T, self.nh, self.hd), ctx.dtype)
+        ops.qk_norm_rope_store(proj[:, :qs], proj[:, qs:qs + kvs], proj[:, qs + kvs:qs + kvs + vs], self.w.get("q_norm"),
+                               self.w.get("k_norm"), self.qk_norm_eps or 0.0, rot.inv_freq if rot and rot.rotary_dim else None,
+                               rot.rotary_dim if rot else 0, q, cache.k, cache.v, cache.block_table, ctx.positions,
+                               ctx.tok_seg, cache.num_pages, ctx.max_positions, ctx.err)
+        attn = ctx.alloc((T, self.nh * self.vhd), ctx.dtype) if self.gate else out
+        ops.masked_attention(ctx, q, attn, cache.k, cache.v, cache.block_table, cache.num_pages, self.mask, self.scale,
+                             self.w.get("sink"))
+        if self.gate:
+            ops.gated_product(attn, proj[:, qs + kvs + vs:], out, "sigmoid", self.out_scale)
+        elif self.out_scale != 1.0:
+            out.mul_(self.out_scale)
+
     def forward(self, ctx, x, cache):
         if self.general:
-            attn = ctx.alloc((x.shape[0], self.nh * self.vhd), x.dtype)
+            attn = ctx.alloc((x.shape[0], self.nh * self.vhd), ctx.dtype)
             self.forward_inner(ctx, x, cache, attn)
             return ops.linear_delta(attn, self.w["o_w"], self.w.get("o_b"))
         T, qs, kvs = x.shape[0], self.q_size, self.kv_size

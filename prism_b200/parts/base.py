@@ -80,8 +80,14 @@ class CacheNeed:
     only the keys of their own block of ``chunk`` positions (counted from 0),
     so the pages of earlier blocks are given back.  ``v_head_dim``: size of a
     value when it differs from a key's (None: the same; 0: no value plane at
-    all, the values are read out of the key rows).  ``state``: one tensor
-    of ``state_shape`` per request, in a slot.  ``none``: nothing."""
+    all, the values are read out of the key rows).  ``keep_first``: under a
+    window, the first ``keep_first`` positions stay visible to every later
+    query, so the pages that hold them are never given back.  ``state``: one
+    tensor of ``state_shape`` per request, in a slot.  ``none``: nothing.
+
+    A mixer that needs several of these (pages for its attention half and
+    state for its recurrent half, or two state tensors of different shapes)
+    lists them in ``Mixer.cache_needs()`` and gets one view for each."""
     kind: str = "none"
     num_kv_heads: int = 0
     head_dim: int = 0
@@ -90,6 +96,7 @@ class CacheNeed:
     state_dtype: str = "float32"
     v_head_dim: Optional[int] = None
     chunk: Optional[int] = None
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:
@@ -97,7 +104,8 @@ class CacheNeed:
 
     def first_kept(self, length: int) -> int:
         """The first position that the query at position ``length`` (the next one of a request holding
-        ``length`` tokens) can still see; everything before it may be given back."""
+        ``length`` tokens) can still see, the kept first positions aside; the pages wholly before it (and
+        wholly after the kept positions) may be given back."""
         lo = 0
         if self.window is not None:
             lo = max(lo, length - self.window + 1)
@@ -107,7 +115,7 @@ class CacheNeed:
 
     def group_key(self):
         return (self.kind, self.num_kv_heads, self.head_dim, self.window,
-                tuple(self.state_shape), self.state_dtype, self.value_dim, self.chunk)
+                tuple(self.state_shape), self.state_dtype, self.value_dim, self.chunk, self.keep_first)
 
 
 @dataclass
@@ -116,16 +124,19 @@ class RotaryParams:
     a float32 table of ``rotary_dim/2`` inverse frequencies on the device."""
     inv_freq: object          # torch.Tensor [rotary_dim // 2] float32
     rotary_dim: int
+    interleaved: bool = False # pairs (2i, 2i + 1) instead of (i, i + rotary_dim / 2)
 
 
 @dataclass(frozen=True)
 class DetachedProjection:
     """A projection that a part hands to the block around it: its weight's file tensors (names relative to
     the block's prefix; several are stacked along dim 0), their biases if any, and its width - the columns
-    it reads (an output projection) or the rows it produces (an input projection)."""
+    it reads (an output projection) or the rows it produces (an input projection).  ``float32``: the part
+    reads its input projection's result in float32 (it feeds norms, gates or a recurrence)."""
     weights: Tuple[WeightSource, ...]
     biases: Tuple[WeightSource, ...]
     width: int
+    float32: bool = False
 
 
 # --------------------------------------------------------------------------
@@ -229,15 +240,25 @@ class Mixer(Part):
     # and every value must come from device arrays.  None: yes unless the mixer keeps per-request state
     # (``cache_need().kind == "state"``); a state mixer that works from ``cache.slots`` alone sets True.
     graph_safe: Optional[bool] = None
+    # True: ``forward`` wants the float32 residual rows themselves as ``x`` where the block has them (a block
+    # whose residual stream is normed), not their copy in the compute dtype.
+    reads_float32 = False
 
     def cache_need(self) -> CacheNeed:
         return CacheNeed()
+
+    def cache_needs(self) -> Tuple[CacheNeed, ...]:
+        """Everything this mixer keeps between steps.  The default is the single ``cache_need()`` (or
+        nothing); a mixer with several needs overrides this, and ``forward`` then gets a tuple of views in
+        the same order instead of one view."""
+        need = self.cache_need()
+        return () if need.kind == "none" else (need,)
 
     def forward(self, ctx, x, cache):
         """``x [T, H]`` normed rows -> ``delta [T, H]`` (or split partial sums
         ``[k, T, H]`` float32) to be added to the residual stream.  ``cache`` is
         the view of this layer's cache plane for this step (``None`` if the
-        mixer needs none)."""
+        mixer needs none; a tuple of views if ``cache_needs()`` lists several)."""
         raise NotImplementedError
 
     # A block that adds the results of several sublayers may take over their last projections and run them
@@ -283,6 +304,9 @@ class Block(Part):
 
     def cache_need(self) -> CacheNeed:
         return self.mixer.cache_need()
+
+    def cache_needs(self) -> Tuple[CacheNeed, ...]:
+        return self.mixer.cache_needs()
 
     def forward(self, ctx, residual, delta, cache):
         raise NotImplementedError

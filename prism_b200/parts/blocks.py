@@ -3,7 +3,9 @@ layer (engine/executor.py:106-127): norm, mixer, residual add, norm,
 feed-forward, residual add.  Each residual add is carried out by the norm
 that follows it (the next block's first norm, or the final norm).
 ``parallel``: one norm whose output both the mixer and the feed-forward read;
-their two results are added to the residual stream together."""
+their two results are added to the residual stream together.
+``postnorm``: the residual stream itself is normed after every sum,
+``x <- norm(alpha x + sublayer(x))``, and the sublayers read x as it is."""
 
 from __future__ import annotations
 
@@ -53,7 +55,7 @@ class ParallelBlock(Block):
             self.out_m, self.out_f = self.mixer.detach_out_projection(), ff.detach_out_projection()
             if self.out_m.biases and self.out_f.biases:
                 raise ValueError("parallel block: at most one of the two output projections may have a bias")
-            if self.mixer.detachable_in and ff.detachable_in:
+            if self.mixer.detachable_in and ff.detachable_in and not getattr(self.mixer, "float32_projection", False):
                 self.in_m, self.in_f = self.mixer.detach_in_projection(), ff.detach_in_projection()
 
     def params(self):
@@ -96,3 +98,41 @@ class ParallelBlock(Block):
         self.mixer.forward_inner(ctx, h, cache, inner[:, :wm], pm)
         self.feed_forward.forward_inner(ctx, h, inner[:, wm:], pf)
         return residual, ops.linear_delta(inner, self.w["out_w"], self.w.get("out_b"), f32=True)
+
+
+@register_part("block", "postnorm")
+class PostNormBlock(Block):
+    """``x <- mixer_norm(alpha * x + mixer(x))``, then ``x <- ff_norm(alpha * x + feed_forward(x))``: the norm
+    comes after the sum and the normed rows are the residual stream, which stays float32; the sublayers read x
+    itself (a mixer with ``reads_float32`` the float32 rows, the others their copy in the compute dtype, which the
+    norm kernel writes beside them).  ``feed_forward`` None: the layer ends after its mixer - unless the model file
+    still has the second norm's weight, in which case that norm is applied to ``alpha * x``."""
+
+    def __init__(self, mixer: PartSpec, mixer_norm: PartSpec, alpha: float = 1.0, feed_forward: Optional[PartSpec] = None,
+                 ff_norm: Optional[PartSpec] = None):
+        self.alpha = float(alpha)
+        self.mixer_norm = self.add_child("mixer_norm", build_part("norm", mixer_norm))
+        self.mixer = self.add_child("mixer", build_part("mixer", mixer))
+        self.feed_forward = (self.add_child("feed_forward", build_part("feed_forward", feed_forward))
+                             if feed_forward is not None else None)
+        self.ff_norm = self.add_child("ff_norm", build_part("norm", ff_norm)) if ff_norm is not None else None
+        if self.feed_forward is not None and self.ff_norm is None:
+            raise ValueError("a postnorm block with a feed-forward needs the norm that follows it")
+
+    def forward(self, ctx, residual, delta, cache):
+        x = residual
+        if delta is not None:                # a block of another kind left its last sum to be done
+            x.add_(delta if delta.dim() == 2 else delta.sum(0))
+        h = ctx.scratch.get("postnorm_rows")
+        if h is None or ctx.scratch.get("postnorm_rows_of") is not x:
+            h = x if ctx.dtype == ops.torch.float32 else x.to(ctx.dtype)
+        d = self.mixer.forward(ctx, x if self.mixer.reads_float32 else h, cache)
+        h = self.mixer_norm.forward_post(ctx, x, d, self.alpha)
+        if self.feed_forward is not None:
+            d = self.feed_forward.forward(ctx, h)
+            h = self.ff_norm.forward_post(ctx, x, d, self.alpha)
+        elif self.ff_norm is not None and self.ff_norm.w.get("weight") is not None:
+            h = self.ff_norm.forward_post(ctx, x, None, self.alpha)
+        # the next block of this kind starts from these rows: no second rounding pass over x
+        ctx.scratch["postnorm_rows"], ctx.scratch["postnorm_rows_of"] = h, x
+        return x, None

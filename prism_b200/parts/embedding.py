@@ -2,20 +2,25 @@
 
 from __future__ import annotations
 
-from .base import Embedding, Head, ParamSpec, WeightSource, register_part
+from typing import Optional
+
+from .base import Embedding, Head, ParamSpec, PartSpec, WeightSource, build_part, register_part
 from .. import ops
 
 
 @register_part("embedding", "token")
 class TokenEmbedding(Embedding):
     """Row gather, times ``scale`` (in float32; 1: no scaling); the output is the
-    float32 residual stream.  ``tensor``: the table's name in the model file."""
+    float32 residual stream.  ``tensor``: the table's name in the model file.  ``norm``: a norm part applied to
+    the gathered rows (in float32, in place)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, tensor: str = "embed_tokens.weight"):
+    def __init__(self, vocab_size: int, hidden_size: int, scale: float = 1.0, tensor: str = "embed_tokens.weight",
+                 norm: Optional[PartSpec] = None):
         self.vocab_size = int(vocab_size)
         self.hidden_size = int(hidden_size)
         self.scale = float(scale)
         self.tensor = tensor
+        self.norm = self.add_child("norm", build_part("norm", norm)) if norm is not None else None
 
     def params(self):
         return [ParamSpec("weight", (WeightSource(self.tensor, (self.vocab_size, self.hidden_size)),))]
@@ -23,6 +28,8 @@ class TokenEmbedding(Embedding):
     def forward(self, ctx):
         out = ctx.alloc((ctx.T, self.hidden_size), ops.torch.float32)
         ops.embed(ctx.token_ids, self.w["weight"], out, ctx.err, self.scale)
+        if self.norm is not None:
+            ops.rms_rows(out, self.norm.w["weight"], self.norm.eps, out)
         return out
 
 

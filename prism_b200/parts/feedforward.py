@@ -11,16 +11,20 @@ from .. import ops
 
 @register_part("feed_forward", "swiglu")
 class SwiGLU(FeedForward):
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    """``names``: the gate, up and down tensors' names in the model file."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int,
+                 names=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
+        self.names = tuple(names)
 
     def params(self):
         H, I = self.hidden_size, self.intermediate_size
         return [
-            ParamSpec("gate_up_w", (WeightSource("gate_proj.weight", (I, H)),
-                                    WeightSource("up_proj.weight", (I, H)))),
-            ParamSpec("down_w", (WeightSource("down_proj.weight", (H, I)),)),
+            ParamSpec("gate_up_w", (WeightSource(self.names[0], (I, H)),
+                                    WeightSource(self.names[1], (I, H)))),
+            ParamSpec("down_w", (WeightSource(self.names[2], (H, I)),)),
         ]
 
     def forward(self, ctx, x):

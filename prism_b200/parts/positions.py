@@ -40,6 +40,52 @@ class RotaryEmbedding(PositionEncoding):
         return self._params
 
 
+@register_part("position", "rotary_scaled")
+class ScaledRotaryEmbedding(PositionEncoding):
+    """Rotation of the first ``rotary_dim`` entries of a head in interleaved pairs (2i, 2i + 1) - or, with
+    ``interleaved`` False, in pairs (i, i + rotary_dim / 2) - by ``position * f_i``, ``f_i = theta^(-2i /
+    rotary_dim)``, with the frequencies rescaled in three bands by wavelength ``l = 2 pi / f`` (``scaling``: a dict
+    ``factor, low, high, original``, or None): unchanged where ``l < original / high``, divided by ``factor`` where
+    ``l > original / low``, and ``(1 - s) f / factor + s f`` with ``s = (original / l - low) / (high - low)`` in
+    between.  The table is float32; the kernels form the angles from it in float32."""
+
+    def __init__(self, rotary_dim: int, theta: float, scaling: dict = None, interleaved: bool = True):
+        self.rotary_dim, self.theta, self.interleaved = int(rotary_dim), float(theta), bool(interleaved)
+        if self.rotary_dim % 2 or self.rotary_dim < 0:
+            raise ValueError(f"rotary_dim {self.rotary_dim} must be even")
+        self.scaling = None
+        if scaling:
+            self.scaling = tuple(float(scaling[k]) for k in ("factor", "low", "high", "original"))
+            if self.scaling[2] == self.scaling[1]:
+                raise ValueError("frequency scaling: 'high' must differ from 'low'")
+        self._params = None
+
+    def frequencies(self) -> torch.Tensor:
+        import math
+        rd = self.rotary_dim
+        f = self.theta ** (-torch.arange(0, rd, 2, dtype=torch.float32) / max(rd, 1))
+        if self.scaling is None:
+            return f
+        factor, low, high, original = self.scaling
+        vals = []
+        for fi in f.tolist():
+            wavelength = 2.0 * math.pi / fi
+            if wavelength < original / high:
+                vals.append(fi)
+            elif wavelength > original / low:
+                vals.append(fi / factor)
+            else:
+                s = (original / wavelength - low) / (high - low)
+                vals.append((1.0 - s) * fi / factor + s * fi)
+        return torch.tensor(vals, dtype=torch.float32)
+
+    def on_bound(self):
+        self._params = RotaryParams(self.frequencies().to(self.device), self.rotary_dim, self.interleaved)
+
+    def rotary(self):
+        return self._params
+
+
 @register_part("position", "none")
 class NoPositionEncoding(PositionEncoding):
     """Keys and queries are used as projected."""

@@ -1,0 +1,260 @@
+"""Recurrent mixers: their memory of a sequence is a float32 matrix per head
+in a state slot of the request, not a cache of keys, so a step costs the same
+at any position.  Everything that enters the recurrences is float32 (the
+input projections give float32 results; decays, gates and unit vectors are
+formed in float32 by the kernels of ``csrc/recurrent.cu``); what leaves for
+the output projection is rounded to the compute dtype once.
+
+``gated_delta``: delta rule with a scalar decay per head and token, behind a
+short causal convolution over time of q, k and v.
+``wkv``: token-shift mixes of the input, a per-channel decay from a low-rank
+product, and a bonus for the current token in the read-out.
+``sum``: several mixers side by side on the same input, their results scaled
+and added (one joint input product and one joint output product where the
+mixers can hand theirs over).
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from ..config.model_config import ConfigError
+from .base import CacheNeed, DetachedProjection, Mixer, ParamSpec, PartSpec, WeightSource, build_part, register_part
+from .. import ops
+
+
+@register_part("mixer", "gated_delta")
+class GatedDeltaMixer(Mixer):
+    """With h the input, per token (``G = num_kv_heads`` q/k heads of ``head_dim``, ``H = num_heads`` value heads of
+    ``v_head_dim``; head i uses q/k head ``i // (H / G)``)::
+
+        q, k, v = silu(conv(W_q h)), silu(conv(W_k h)), silu(conv(W_v h))     conv: causal over time, per channel
+        q <- q / sqrt(sum q^2 + unit_eps) / sqrt(head_dim);   k <- k / sqrt(sum k^2 + unit_eps)      per head
+        beta = sigmoid(W_b h);   g = exp(-exp(A_log) softplus(W_a h + dt_bias))                     per head
+        S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q                              per head
+        out = W_o [o / rms(o) * norm * silu(W_g h)]
+
+    State per request: S ``[H, v_head_dim, head_dim]`` (stored column by column) and the convolution's last
+    ``conv - 1`` inputs ``[conv - 1, channels]``, both float32, both starting at zero.  ``names``: the tensors'
+    names in the model file (keys q, k, v, q_conv, k_conv, v_conv, b, a, A_log, dt_bias, g, norm, o)."""
+
+    NAMES = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", q_conv="q_conv.weight", k_conv="k_conv.weight",
+                 v_conv="v_conv.weight", b="b_proj.weight", a="a_proj.weight", A_log="A_log", dt_bias="dt_bias",
+                 g="g_proj.weight", norm="norm.weight", o="o_proj.weight")
+    graph_safe = True            # works from the device's slot array alone
+    float32_projection = True
+    detachable_out = detachable_in = True
+
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, conv: int,
+                 eps: float, unit_eps: float = 1e-6, out_scale: float = 1.0, names: Optional[dict] = None):
+        self.hidden_size, self.H, self.G = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dk, self.dv, self.K = int(head_dim), int(v_head_dim), int(conv)
+        if min(self.H, self.G, self.dk, self.dv, self.K) < 1 or self.H % self.G:
+            raise ConfigError(f"gated delta mixer: heads {self.H} must be a multiple of kv_heads {self.G}, and heads, "
+                              f"sizes and the convolution's taps positive")
+        if self.dk > 1024:
+            raise ConfigError(f"gated delta mixer: head_dim {self.dk} exceeds the scan kernel's 1024")
+        self.eps, self.unit_eps, self.out_scale = float(eps), float(unit_eps), float(out_scale)
+        self.names = dict(self.NAMES, **(names or {}))
+        self.C = 2 * self.G * self.dk + self.H * self.dv          # channels of the convolution: q | k | v
+        self.b_off, self.a_off, self.g_off = self.C, self.C + self.H, self.C + 2 * self.H
+        self.in_width = self.C + 2 * self.H + self.H * self.dv    # q | k | v | b | a | g
+        self._own_in = self._own_out = True
+
+    def cache_needs(self):
+        return (CacheNeed("state", state_shape=(self.H, self.dv, self.dk)),
+                CacheNeed("state", state_shape=(self.K - 1, self.C)))
+
+    def _in_sources(self):
+        W, n, G, H, dk, dv = self.hidden_size, self.names, self.G, self.H, self.dk, self.dv
+        return (WeightSource(n["q"], (G * dk, W)), WeightSource(n["k"], (G * dk, W)), WeightSource(n["v"], (H * dv, W)),
+                WeightSource(n["b"], (H, W)), WeightSource(n["a"], (H, W)), WeightSource(n["g"], (H * dv, W)))
+
+    def _out_source(self):
+        return WeightSource(self.names["o"], (self.hidden_size, self.H * self.dv))
+
+    def params(self):
+        n, G, H, dk, dv, K = self.names, self.G, self.H, self.dk, self.dv, self.K
+        ps = [ParamSpec("in_w", self._in_sources())] if self._own_in else []
+        ps += [ParamSpec("taps", (WeightSource(n["q_conv"], (G * dk, K)), WeightSource(n["k_conv"], (G * dk, K)),
+                                  WeightSource(n["v_conv"], (H * dv, K)))),
+               ParamSpec("A_log", (WeightSource(n["A_log"], (H,), "bias"),)),
+               ParamSpec("dt_bias", (WeightSource(n["dt_bias"], (H,), "bias"),)),
+               ParamSpec("norm", (WeightSource(n["norm"], (dv,), "norm"),))]
+        if self._own_out:
+            ps.append(ParamSpec("o_w", (self._out_source(),)))
+        return ps
+
+    def detach_out_projection(self):
+        self._own_out = False
+        return DetachedProjection(self.handed_over(self._out_source()), (), self.H * self.dv)
+
+    def detach_in_projection(self):
+        self._own_in = False
+        return DetachedProjection(self.handed_over(*self._in_sources()), (), self.in_width, float32=True)
+
+    def forward_inner(self, ctx, x, cache, out, proj=None):
+        state, tail = cache
+        T, H, G, dk, dv = x.shape[0], self.H, self.G, self.dk, self.dv
+        if proj is None:
+            proj = ops.linear(x, self.w["in_w"], None, out_dtype=torch.float32)
+        qkv = ctx.alloc((T, self.C), torch.float32)
+        bg = ctx.alloc((T, 2 * H), torch.float32)
+        ops.conv_unit_gates(proj, self.b_off, self.a_off, self.w["taps"], tail.state, self.w["A_log"], self.w["dt_bias"],
+                            ctx, G, H, dk, dv, self.unit_eps, qkv, bg)
+        ops.state_tail(proj, tail.state, ctx)
+        o = ctx.alloc((T, H, dv), torch.float32)
+        ops.recurrent_scan(ops.SCAN_DELTA, qkv, 0, G * dk, 2 * G * dk, state.state, ctx, H, H // G, dk, dv, o, bg=bg)
+        ops.headnorm_gate(o, proj[:, self.g_off:self.g_off + H * dv], self.w["norm"], self.eps, self.out_scale, out)
+
+    def forward(self, ctx, x, cache):
+        inner = ctx.alloc((x.shape[0], self.H * self.dv), ctx.dtype)
+        self.forward_inner(ctx, x, cache, inner)
+        return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
+
+
+@register_part("mixer", "wkv")
+class WKVMixer(Mixer):
+    """With x the input and x' the previous token's input (zeros before the first token), ``mix_s = x + (x' - x)
+    mu_s`` for s in r, k, v, g, w; per head of ``head_dim`` channels::
+
+        r, k, v = W_r mix_r, W_k mix_k, W_v mix_v;   gate = silu(W_g mix_g)
+        w = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0))                         per key channel
+        o = (S + diag(u) k v^T)^T r;   S <- diag(w) S + k v^T              u: a bonus for the current token only
+        out = W_o [o / rms(o) * norm * gate]
+
+    State per request: S ``[H, head_dim, head_dim]`` and the previous token's input ``[1, hidden]``, float32,
+    starting at zero.  The mixes are formed from the float32 input rows.  ``names``: keys mu_r, mu_k, mu_v, mu_g,
+    mu_w, r, k, v, g, w1, w2, w0, u, norm, o."""
+
+    NAMES = dict(mu_r="mu.r", mu_k="mu.k", mu_v="mu.v", mu_g="mu.g", mu_w="mu.w", r="r", k="k", v="v", g="g", w1="w1",
+                 w2="w2", w0="w0", u="u", norm="norm", o="o")
+    graph_safe = True
+    reads_float32 = True
+
+    def __init__(self, hidden_size: int, num_heads: int, head_dim: int, decay_rank: int, eps: float,
+                 out_scale: float = 1.0, names: Optional[dict] = None):
+        self.hidden_size, self.H, self.d, self.rank = int(hidden_size), int(num_heads), int(head_dim), int(decay_rank)
+        if min(self.H, self.d, self.rank) < 1 or self.d > 1024:
+            raise ConfigError("wkv mixer: heads, head size and the decay's rank must be positive, the head size at most 1024")
+        self.eps, self.out_scale = float(eps), float(out_scale)
+        self.names = dict(self.NAMES, **(names or {}))
+
+    def cache_needs(self):
+        return (CacheNeed("state", state_shape=(self.H, self.d, self.d)),
+                CacheNeed("state", state_shape=(1, self.hidden_size)))
+
+    def params(self):
+        W, n, A, R = self.hidden_size, self.names, self.H * self.d, self.rank
+        return [ParamSpec("mu", tuple(WeightSource(n["mu_" + s], (W,), "bias") for s in "rkvgw")),
+                ParamSpec("rkvg_w", tuple(WeightSource(n[s], (A, W)) for s in "rkvg")),
+                ParamSpec("w1", (WeightSource(n["w1"], (R, W)),)),
+                ParamSpec("w2", (WeightSource(n["w2"], (A, R)),)),
+                ParamSpec("w0", (WeightSource(n["w0"], (A,), "bias"),)),
+                ParamSpec("u", (WeightSource(n["u"], (self.H, self.d), "bias"),)),
+                ParamSpec("norm", (WeightSource(n["norm"], (A,), "norm"),)),
+                ParamSpec("o_w", (WeightSource(n["o"], (W, A)),))]
+
+    def on_bound(self):
+        # the decay's second product runs in float32 whatever the engine's dtype (its input is the float32 tanh)
+        self.w2_f32 = self.w["w2"].float() if self.w["w2"] is not None else None
+        self.mu = self.w["mu"].view(5, self.hidden_size)
+
+    def forward(self, ctx, x, cache):
+        state, prev = cache
+        T, W, H, d, A = x.shape[0], self.hidden_size, self.H, self.d, self.H * self.d
+        if x.dtype != torch.float32:
+            x = x.float()
+        mixes = ctx.alloc((5, T, W), ctx.dtype)
+        ops.shift_mix(x, prev.state, self.mu, ctx, mixes)
+        ops.state_tail(x, prev.state, ctx)
+        proj = ctx.alloc((4, T, A), torch.float32)             # r, k, v, g: each from its own mix, one matrix each
+        for i in range(4):
+            ops.linear(mixes[i], self.w["rkvg_w"][i * A:(i + 1) * A], None, out=proj[i])
+        low = ops.linear(mixes[4], self.w["w1"], None, out_dtype=torch.float32)
+        ops.activation(low, low, "tanh")
+        ww = ops.linear(low, self.w2_f32, None, out_dtype=torch.float32)
+        o = ctx.alloc((T, H, d), torch.float32)
+        # the scan addresses rows as base + t * stride + offset: r, k and v are T * A elements apart
+        ops.recurrent_scan(ops.SCAN_BONUS, proj[0], 0, T * A, 2 * T * A, state.state, ctx, H, 1, d, d, o,
+                           ww=ww, w0=self.w["w0"], u=self.w["u"])
+        inner = ctx.alloc((T, A), ctx.dtype)
+        ops.headnorm_gate(o, proj[3], self.w["norm"], self.eps, self.out_scale, inner)
+        return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
+
+
+@register_part("mixer", "sum")
+class SumOfMixers(Mixer):
+    """``sum_i scale_i * mixer_i(h)``: mixers side by side on the same input.  ``prefixes``: each mixer's tensors
+    sit under its own prefix inside this part's.  Where every mixer hands over its output projection, the sum is
+    one product over the joined inner outputs, ``[a_1 | a_2 | ..] @ [W_o1 | W_o2 | ..]^T`` with each scale folded
+    into its ``a_i``, so the results are added in the product's float32 accumulator; where every mixer also hands
+    over its input projection, those are one product too (float32 results if any of them wants that).  ``fuse``
+    False: every mixer runs on its own and the float32 results are added."""
+
+    graph_safe = True
+
+    def __init__(self, mixers: Sequence[PartSpec], scales: Sequence[float], fuse: bool = True):
+        if len(mixers) != len(scales) or not mixers:
+            raise ConfigError("a sum of mixers needs one scale for each mixer")
+        self.scales = [float(s) for s in scales]
+        self.mixers = [self.add_child(f"m{i}", build_part("mixer", spec)) for i, spec in enumerate(mixers)]
+        self.n_needs = [len(m.cache_needs()) for m in self.mixers]
+        self.outs = self.ins = None
+        if fuse and all(m.detachable_out for m in self.mixers):
+            for m, s in zip(self.mixers, self.scales):
+                m.out_scale = s
+            self.outs = [m.detach_out_projection() for m in self.mixers]
+            if any(d.biases for d in self.outs):
+                raise ConfigError("a fused sum of mixers takes output projections without bias")
+            if all(m.detachable_in for m in self.mixers):
+                self.ins = [m.detach_in_projection() for m in self.mixers]
+                if any(d.biases for d in self.ins):
+                    raise ConfigError("a fused sum of mixers takes input projections without bias")
+        self.reads_float32 = False
+
+    def cache_needs(self):
+        return tuple(n for m in self.mixers for n in m.cache_needs())
+
+    def params(self):
+        ps = []
+        if self.ins is not None:
+            ps.append(ParamSpec("in_w", tuple(w for d in self.ins for w in d.weights)))
+        if self.outs is not None:
+            ps.append(ParamSpec("out_w", tuple(w for d in self.outs for w in d.weights), axis=1))
+        return ps
+
+    def _caches(self, cache):
+        views = cache if isinstance(cache, tuple) else (() if cache is None else (cache,))
+        out, o = [], 0
+        for n in self.n_needs:
+            out.append(None if n == 0 else (views[o] if n == 1 else tuple(views[o:o + n])))
+            o += n
+        return out
+
+    def forward(self, ctx, x, cache):
+        caches = self._caches(cache)
+        T = x.shape[0]
+        if self.outs is None:
+            total = None
+            for m, s, c in zip(self.mixers, self.scales, caches):
+                d = m.forward(ctx, x, c)
+                d = (d if d.dim() == 2 else d.sum(0)).float() * s
+                total = d if total is None else total.add_(d)
+            return total
+        inner = ctx.alloc((T, sum(d.width for d in self.outs)), ctx.dtype)
+        projs = [None] * len(self.mixers)
+        if self.ins is not None:
+            f32 = any(d.float32 for d in self.ins)
+            proj = ops.linear(x, self.w["in_w"], None, out_dtype=torch.float32 if f32 else None)
+            o = 0
+            for i, d in enumerate(self.ins):
+                projs[i] = proj[:, o:o + d.width]
+                o += d.width
+        o = 0
+        for m, d, c, p in zip(self.mixers, self.outs, caches, projs):
+            m.forward_inner(ctx, x, c, inner[:, o:o + d.width], p)
+            o += d.width
+        return ops.linear_delta(inner, self.w["out_w"], None, f32=True)

@@ -167,6 +167,12 @@ def load_model_folder(model_dir: str, device, dtype: torch.dtype):
     """``(typed config, bound model, pool)`` for a folder; the model class is
     chosen by config.json's ``architectures``."""
     raw = read_config_json(model_dir)
-    cfg, model = build_model(raw)
+    shapes = {}
+    try:
+        for p in find_shards(model_dir):
+            shapes.update({name: meta[0] for name, meta in read_safetensors_header(p).items()})
+    except FileNotFoundError:
+        shapes = None               # load_weights raises with the folder's name
+    cfg, model = build_model(raw, shapes)
     pool = load_weights(model, model_dir, device, dtype)
     return cfg, model, pool

@@ -31,8 +31,8 @@ STD = 0.02
 def file_tensors(model) -> Iterator[Tuple[str, tuple, str]]:
     """``(tensor name, shape, init kind)`` of every tensor a model file holds."""
     for _, spec in model.named_params():
-        if spec.optional and spec.alias_of:
-            continue                      # a tied head has no tensor of its own
+        if spec.optional:
+            continue                      # a tied head has no tensor of its own; other optional tensors are left out
         for s in spec.sources:
             yield s.name, tuple(s.shape), s.init
 
@@ -72,7 +72,7 @@ def write_model_folder(raw_config: dict, seed: int, out_dir: str,
 def random_pool(model, seed: int, device, compute_dtype: torch.dtype) -> StaticWeightPool:
     """Allocate a pool in ``compute_dtype`` and fill it on the device."""
     named = list(model.named_params())
-    plan = [(q, s, None if (s.optional and s.alias_of) else compute_dtype) for q, s in named]
+    plan = [(q, s, None if s.optional else compute_dtype) for q, s in named]
     pool = StaticWeightPool(plan, device)
     idx = 0
     for q, spec, dt in plan:
