@@ -492,7 +492,7 @@ def main():
     ap.add_argument("--model", default="7b", choices=sorted(SHAPES), help="layer sizes (default: the headline's)")
     ap.add_argument("--prompt-len", type=int, default=2048, help="prompt tokens (context = twice as many)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
-    ap.add_argument("--design", default=None, choices=["dolezen"],
+    ap.add_argument("--design", default=None, choices=["dolezen", "pofazen"],
                     help="instead of the headline: prefill and decode throughput of this design beside Qwen2 at equal "
                          "size, with the attention kernels of both (benchmarks/design_bench.py)")
     ap.add_argument("--sizes", default="2k,4k", help="with --design: the layer sizes to measure")
@@ -508,7 +508,8 @@ def main():
         from benchmarks import design_bench
         pk = peaks()
         print(json.dumps(design_bench.run(args.sizes.split(","), min(args.steps, 64), args.warmup, batch=args.batch,
-                                          peaks=dict(hbm_gbs=pk["hbm_gbs"], bf16_tflops=pk["bf16_tflops"], source=pk["source"]))))
+                                          peaks=dict(hbm_gbs=pk["hbm_gbs"], bf16_tflops=pk["bf16_tflops"], source=pk["source"]),
+                                          design=args.design)))
         return 0
     if args.prompt_len % PAGE:
         ap.error(f"--prompt-len must be a multiple of the page size {PAGE}")

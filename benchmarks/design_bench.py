@@ -1,9 +1,9 @@
-"""Prefill and decode throughput of the Dolezen design at layer sizes that resemble real models (random
-weights, bf16), beside the Qwen2 architecture at equal width, depth and parameter count, and the attention
-kernels of both on the same problem with their fractions of the measured peaks.
+"""Prefill and decode throughput of the Dolezen or the Pofazen design at layer sizes that resemble real models
+(random weights, bf16), beside the Qwen2 architecture at equal width, depth and parameter count, and the
+design's own kernels beside Qwen2's on the same problem with their fractions of the measured peaks.
 
-    python bench.py --design dolezen [--sizes 2k,4k] [--steps K] [--warmup W]
-    python benchmarks/design_bench.py [--sizes 2k] [--kernels-only] [--once KERNEL]
+    python bench.py --design dolezen|pofazen [--sizes 2k,4k] [--steps K] [--warmup W]
+    python benchmarks/design_bench.py [--design pofazen] [--sizes 2k] [--kernels-only] [--once KERNEL]
 
 One JSON line.  Timing: CUDA events after W >= 3 warm-up runs; every timed step reads all weights (more than
 the 126 MB L2) and the kernel timings flush L2 between launches.
@@ -51,6 +51,22 @@ def dolezen_config(s):
             layers.append(dict(type="attention", mixer=dict(att), mlp=mlp))
     return dict(architecture="Dolezen", vocab=s["vocab"], width=s["width"], norm=dict(eps=1e-6),
                 embedding=dict(scale=1.0), layers=layers, max_positions=8192)
+
+
+def pofazen_config(s):
+    """Layers: parallel (windowed attention that keeps the first tokens + gated delta rule), wkv, wkv, parallel, ...;
+    every layer with a gated feed-forward of Qwen2's size."""
+    left = dict(heads=s["heads"], kv_heads=s["kv_heads"], dim=s["dim"], vdim=s["vdim"], scale=s["dim"] ** -0.5,
+                mask=dict(size=s["window"], keep_first=4),
+                rot=dict(base=10000.0, dims=s["dim"] // 2, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    right = dict(heads=s["heads"], kv_heads=s["kv_heads"], dim=s["dim"], vdim=s["vdim"], conv=4)
+    par = dict(left=left, right=right, left_scale=1.0, right_scale=1.0)
+    wkv = dict(heads=s["width"] // 64, dim=64, decay_rank=64)
+    mlp = dict(kind="dense", ff=s["ff"] * 2 // 3 // 256 * 256)
+    layers = [dict(type="parallel", mixer=par, mlp=mlp) if i % 4 in (0, 3) else dict(type="wkv", mixer=wkv, mlp=mlp)
+              for i in range(s["layers"])]
+    return dict(architecture="Pofazen", vocab=s["vocab"], width=s["width"], norm=dict(eps=1e-6), postln_alpha=2.0,
+                layers=layers, max_positions=8192)
 
 
 def qwen2_config(s):
@@ -219,9 +235,104 @@ def kernel_numbers(s, pk, once=None):
     return out
 
 
-def run(sizes, steps, warmup, prompt_len=2048, batch=8, kernels_only=False, once=None, peaks=None):
+def _rates(ms, flops, nbytes, pk):
+    return dict(us=round(ms * 1e3, 1), tflops=round(flops / ms / 1e9, 2),
+                frac_bf16_peak_of_measured=round(flops / ms / 1e9 / pk["bf16_tflops"], 4), gbs=round(nbytes / ms / 1e6, 1),
+                frac_hbm_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4))
+
+
+def pofazen_kernel_numbers(s, pk, once=None):
+    """The design's kernels alone: attention under a window that keeps the first tokens against Qwen2's
+    kernels under the same window (same head shape), and the two recurrent scans (prefill of 2,048 tokens: float32
+    FMA work, one token after another; decode: the float32 state read and written once a step)."""
+    from prism_b200 import ops
+    out = {}
+    T = 2048
+    nh, nkv, dk, dv, win = s["heads"], s["kv_heads"], s["dim"], s["vdim"], s["window"]
+    mask = ops.KeyMask.window(win, 4)
+    shapes = (("prefill_2048", 1, 0, T), ("decode_b8", 8, T - 1, 1), ("decode_b64", 64, T - 1, 1))
+    for label, batch, cached, q_len in shapes:
+        name = f"window_keep_{label}"
+        if once and once != name:
+            continue
+        c, kc, vc, bt, npages = paged(batch, cached, q_len, nkv, dk, dv)
+        q = torch.randn(batch * q_len, nh, dk, device=DEV, dtype=torch.bfloat16)
+        o = torch.empty(batch * q_len, nh * dv, device=DEV, dtype=torch.bfloat16)
+        fn = lambda: ops.masked_attention(c, q, o, kc, vc, bt, npages, mask, dk ** -0.5, None)
+        if once:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            return {}
+        ms = timeit(fn)
+        pairs = batch * sum(min(p + 1, win) + min(4, max(0, p + 1 - win)) for p in range(cached, cached + q_len))
+        keys = batch * (min(cached + q_len, win + 4) if q_len == 1 else cached + q_len)
+        out[name] = _rates(ms, 2 * pairs * nh * (dk + dv), 2 * (keys * nkv * (dk + dv) + batch * q_len * nh * (dk + dv)), pk)
+    for label, batch, cached, q_len in shapes:          # the closest model's kernels under the same window, no kept tokens
+        if once:
+            break
+        c, kc, vc, bt, npages = paged(batch, cached, q_len, nkv, dk, dk)
+        q = torch.randn(batch * q_len, nh, dk, device=DEV, dtype=torch.bfloat16)
+        o = torch.empty(batch * q_len, nh * dk, device=DEV, dtype=torch.bfloat16)
+        if q_len == 1:
+            ns = ops.decode_splits(batch, nkv, cached + 1, win)
+            po = torch.empty(batch, nh, ns, dk, device=DEV)
+            pml = torch.empty(batch, nh, ns, 2, device=DEV)
+            variants = [("qwen2_window", lambda: ops.attention_decode_bf16(q, o, kc, vc, bt, c.positions, c.tok_seg, npages, win,
+                                                                           dk ** -0.5, ns, po, pml, c.err))]
+        else:
+            variants = [("qwen2_window_tcgen05", lambda: ops.attention_prefill_tc(q, o, kc, vc, bt, c.seg_start, c.cached_len, q_len,
+                                                                                  npages, win, dk ** -0.5, c.err)),
+                        ("qwen2_window_mma_sync", lambda: ops.attention_prefill_bf16(q, o, kc, vc, bt, c.seg_start, c.cached_len,
+                                                                                     q_len, npages, win, dk ** -0.5, c.err))]
+        for vname, fn in variants:
+            ms = timeit(fn)
+            pairs = batch * sum(min(p + 1, win) for p in range(cached, cached + q_len))
+            keys = batch * (min(cached + q_len, win) if q_len == 1 else cached + q_len)
+            out[f"{vname}_{label}"] = _rates(ms, 4 * pairs * nh * dk, 2 * (keys * nkv * 2 * dk + 2 * batch * q_len * nh * dk), pk)
+    # the recurrent scans
+    wh, wd = s["width"] // 64, 64
+    for sname, mode, H, rep, kd, vd in (("delta_scan", ops.SCAN_DELTA, nh, nh // nkv, dk, dv), ("bonus_scan", ops.SCAN_BONUS, wh, 1, wd, wd)):
+        for label, batch, cached, q_len in shapes:
+            name = f"{sname}_{label}"
+            if once and once != name:
+                continue
+            Tt = batch * q_len
+            G = H // rep
+            c = types.SimpleNamespace(seg_start=(torch.arange(batch + 1, dtype=torch.int32) * q_len).to(DEV),
+                                      state_slots=torch.arange(batch, dtype=torch.int32, device=DEV), S=batch)
+            state = torch.zeros(batch + 1, H, vd, kd, device=DEV)
+            o = torch.empty(Tt, H, vd, device=DEV)
+            if mode == ops.SCAN_DELTA:
+                x = torch.nn.functional.normalize(torch.randn(Tt, 2 * G + H, kd, device=DEV), dim=-1).view(Tt, -1)
+                bg = torch.rand(Tt, 2 * H, device=DEV) * 0.5 + 0.5
+                fn = lambda: ops.recurrent_scan(mode, x, 0, G * kd, 2 * G * kd, state, c, H, rep, kd, vd, o, bg=bg)
+            else:
+                x = torch.randn(Tt, 3 * H * kd, device=DEV) * 0.1
+                ww = torch.randn(Tt, H * kd, device=DEV)
+                w0, u = torch.zeros(H * kd, device=DEV), torch.randn(H * kd, device=DEV) * 0.1
+                fn = lambda: ops.recurrent_scan(mode, x, 0, H * kd, 2 * H * kd, state, c, H, 1, kd, vd, o, ww=ww, w0=w0, u=u)
+            if once:
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                return {}
+            ms = timeit(fn)
+            flops = 6 * Tt * H * kd * vd                    # three multiply-adds per state entry and token
+            nbytes = 4 * (2 * batch * H * kd * vd + Tt * H * (2 * kd + 2 * vd))
+            out[name] = dict(us=round(ms * 1e3, 1), fp32_tflops=round(flops / ms / 1e9, 2), gbs=round(nbytes / ms / 1e6, 1),
+                             frac_hbm_of_measured=round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4),
+                             us_per_token=round(ms * 1e3 / q_len, 3))
+    return out
+
+
+DESIGNS = {"dolezen": (dolezen_config, kernel_numbers), "pofazen": (pofazen_config, pofazen_kernel_numbers)}
+
+
+def run(sizes, steps, warmup, prompt_len=2048, batch=8, kernels_only=False, once=None, peaks=None, design="dolezen"):
     pk = peaks or dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
-    result = dict(metric="prefill and decode tokens/s, Dolezen beside Qwen2 at equal size", unit="tokens/s", n_gpus=1,
+    make_config, design_kernels = DESIGNS[design]
+    result = dict(metric=f"prefill and decode tokens/s, {design.capitalize()} beside Qwen2 at equal size", unit="tokens/s", n_gpus=1,
                   steps=steps, warmup=warmup, dtype="bf16", data="synthetic (random weights, random token ids)",
                   peaks=pk, sizes={})
     launches = 0
@@ -229,13 +340,13 @@ def run(sizes, steps, warmup, prompt_len=2048, batch=8, kernels_only=False, once
         s = SIZES[name]
         entry = dict(shape=s)
         if not kernels_only and not once:
-            for label, raw in (("dolezen", dolezen_config(s)), ("qwen2", qwen2_config(s))):
+            for label, raw in ((design, make_config(s)), ("qwen2", qwen2_config(s))):
                 entry[label] = engine_numbers(raw, prompt_len, batch, steps, warmup)
                 launches += entry[label].pop("launches")
-            entry["dolezen_over_qwen2"] = dict(
-                prefill=round(entry["dolezen"]["prefill_tokens_per_s"] / entry["qwen2"]["prefill_tokens_per_s"], 3),
-                decode=round(entry["dolezen"]["decode_tokens_per_s"] / entry["qwen2"]["decode_tokens_per_s"], 3))
-        entry["kernels"] = kernel_numbers(s, pk, once)
+            entry[f"{design}_over_qwen2"] = dict(
+                prefill=round(entry[design]["prefill_tokens_per_s"] / entry["qwen2"]["prefill_tokens_per_s"], 3),
+                decode=round(entry[design]["decode_tokens_per_s"] / entry["qwen2"]["decode_tokens_per_s"], 3))
+        entry["kernels"] = design_kernels(s, pk, once)
         result["sizes"][name] = entry
     result["gpu_launches"] = launches
     result["config"] = dict(prompt_len=prompt_len, decode_batch=batch, page_size=PAGE, l2="inputs larger than L2 (weights); "
@@ -245,13 +356,15 @@ def run(sizes, steps, warmup, prompt_len=2048, batch=8, kernels_only=False, once
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
+    ap.add_argument("--design", default="dolezen", choices=sorted(DESIGNS))
     ap.add_argument("--sizes", default="2k,4k")
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--kernels-only", action="store_true")
     ap.add_argument("--once", default=None, help="launch one kernel case a few times without timing (for a profiler)")
     a = ap.parse_args(argv)
-    print(json.dumps(run(a.sizes.split(","), a.steps, max(3, a.warmup), kernels_only=a.kernels_only, once=a.once)))
+    print(json.dumps(run(a.sizes.split(","), a.steps, max(3, a.warmup), kernels_only=a.kernels_only, once=a.once,
+                         design=a.design)))
 
 
 if __name__ == "__main__":

@@ -20,7 +20,7 @@
 //   * prism_shift_mix        x + (x_prev - x) mu_s for several mu at once (x_prev of a step's first token comes
 //     from the state);
 //   * prism_headnorm_gate    o / rms(o) per head, times a weight, times silu(gate), times a constant.
-#include "common.cuh"
+#include "mma_helpers.cuh"
 
 #define PRISM_SCAN_DELTA 0
 #define PRISM_SCAN_BONUS 1
@@ -143,19 +143,21 @@ __global__ void headnorm_gate_kernel(const float* __restrict__ o_in, const float
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// The scan.  grid (heads, segments, column blocks); a thread owns R rows (i = part + L n) of one column of S,
-// the L threads of a column are neighbouring lanes of a warp and add up their partial dot products by shuffles.
-// The step's vectors come through shared memory TB tokens at a time.  The state is kept in memory as
-// [slot][head][column][row], so that the L threads of a column read neighbouring floats.
-//   SCAN_DELTA:  qk [T, *] row stride qs: q of kv head g at qo + g dk, k at ko + g dk; v at vo + h dv;
+// The scan.  grid (heads, segments, column blocks); the L threads of a column are neighbouring lanes of a warp,
+// each owns R rows of that column of S in registers - quads of four neighbouring rows, quad part + L m - and
+// they add up their partial dot products by shuffles.  The step's vectors come through shared memory TB tokens
+// at a time with cp.async, the next block on its way while this one is worked on; a thread reads its quads
+// of q, k (w, u) with 128-bit loads.  The state is kept in memory as [slot][head][column][row], so that the
+// threads of a column read neighbouring floats.
+//   SCAN_DELTA:  x [T, *] row stride xs: q of kv head g at qo + g dk, k at ko + g dk; v at vo + h dv;
 //                bg [T, 2 H]: beta | g.
-//   SCAN_BONUS:  r at qo + h dk, k at ko + h dk, v at vo + h dv (dk == dv there), the decay's exponent ww
-//                [T, H dk] (row stride ws) with w = exp(-exp(ww + w0)), w0 [H dk], bonus u [H dk].
+//   SCAN_BONUS:  r at qo + h dk, k at ko + h dk, v at vo + h dv, the decay's exponent ww [T, H dk] (row stride ws)
+//                with w = exp(-exp(ww + w0)) formed in shared memory, w0 [H dk], bonus u [H dk].
 // ---------------------------------------------------------------------------------------------------------
 struct ScanArgs {
     const float* x;          // q | k | v (or r | k | v) rows
     long long xs;
-    int qo, ko, vo;
+    long long qo, ko, vo;
     const float* bg;         // DELTA: beta | g
     const float* ww;         // BONUS: the decay's exponent before w0
     long long ws;
@@ -167,17 +169,26 @@ struct ScanArgs {
     const int* seg_start;
     const int* slots;
     float* out;              // [T, H, dv]
-    int H, rep, dk, dv, cols, L, TB;
+    int H, rep, dk, dkp, dv, cols, colsp, L, TB;
+    int vec;                 // every source row piece starts on 16 bytes and is whole quads long
 };
+
+__device__ __forceinline__ void cp_async_f(float* smem, const float* gmem, int floats) {      // 1 or 4 floats
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+    if (floats == 4) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem));
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(gmem));
+}
 
 template <int MODE, int R>
 __global__ void scan_kernel(const ScanArgs a) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
+    constexpr int NV = MODE == PRISM_SCAN_BONUS ? 3 : 2;       // vectors over the key channels per token
+    constexpr int Q = R / 4;                                   // quads of rows a thread owns
     const int h = blockIdx.x, seg = blockIdx.y, col0 = blockIdx.z * a.cols;
     const int s0 = a.seg_start[seg], qlen = a.seg_start[seg + 1] - s0;
-    const int L = a.L, dk = a.dk, dv = a.dv, TB = a.TB;
+    const int L = a.L, dk = a.dk, dkp = a.dkp, dv = a.dv, TB = a.TB;
     const int ncols = min(a.cols, dv - col0);
     // the block is a whole number of warps: threads beyond the CTA's columns run along (they take part in the
     // shuffles) and neither load nor store
@@ -185,101 +196,164 @@ __global__ void scan_kernel(const ScanArgs a) {
     const bool live = (int)threadIdx.x / L < ncols;
     const int lc = live ? threadIdx.x / L : 0, col = col0 + lc;
     const int kvh = h / a.rep;                         // DELTA: the q/k head this head uses
-    // shared: per token of the block  first[dk] (q or r) | second[dk] (k) | third[dk] (BONUS: w) | v[cols] | 2 scalars
-    const int per_tok = (MODE == PRISM_SCAN_BONUS ? 3 : 2) * dk + a.cols + 2;
-    float* ub = sm + (size_t)TB * per_tok;             // BONUS: u[dk]
-    float S[R];
-    float* st = a.state + (((size_t)a.slots[seg] * a.H + h) * dv + (live ? col : 0)) * dk;
-#pragma unroll
-    for (int n = 0; n < R; ++n) {
-        const int i = part + L * n;
-        S[n] = (live && i < dk) ? st[i] : 0.f;
-    }
-    if (MODE == PRISM_SCAN_BONUS)
-        for (int i = threadIdx.x; i < dk; i += blockDim.x) ub[i] = load_param(a.u, a.u_bf16, (size_t)h * dk + i);
+    // shared, per token of a block:  first[dkp] (q or r) | second[dkp] (k) | third[dkp] (BONUS: w) | v[colsp] | 4 scalars
+    const int per_tok = NV * dkp + a.colsp + 4;
+    float* ub = sm + (size_t)2 * TB * per_tok;         // BONUS: u[dkp]
     const float* x = pdl_fresh(a.x);
     const float* bg = pdl_fresh(a.bg);
     const float* ww = pdl_fresh(a.ww);
 
-    for (int b0 = 0; b0 < qlen; b0 += TB) {
-        const int nb = min(TB, qlen - b0);
-        __syncthreads();                               // the block before this one has been used up
-        for (int idx = threadIdx.x; idx < nb * per_tok; idx += blockDim.x) {
-            const int tt = idx / per_tok, c = idx - tt * per_tok;
-            const size_t t = (size_t)(s0 + b0 + tt);
-            float v;
-            if (MODE == PRISM_SCAN_DELTA) {
-                if (c < dk) v = x[t * a.xs + a.qo + kvh * dk + c];
-                else if (c < 2 * dk) v = x[t * a.xs + a.ko + kvh * dk + (c - dk)];
-                else if (c < 2 * dk + a.cols) v = (c - 2 * dk) < ncols ? x[t * a.xs + a.vo + h * dv + col0 + (c - 2 * dk)] : 0.f;
-                else v = bg[t * 2 * a.H + (c - 2 * dk - a.cols) * a.H + h];          // beta, then g
-            } else {
-                if (c < dk) v = x[t * a.xs + a.qo + h * dk + c];
-                else if (c < 2 * dk) v = x[t * a.xs + a.ko + h * dk + (c - dk)];
-                else if (c < 3 * dk) {
-                    const int i = c - 2 * dk;
-                    v = expf(-expf(ww[t * a.ws + h * dk + i] + load_param(a.w0, a.w0_bf16, (size_t)h * dk + i)));
-                } else if (c < 3 * dk + a.cols) v = (c - 3 * dk) < ncols ? x[t * a.xs + a.vo + h * dv + col0 + (c - 3 * dk)] : 0.f;
-                else v = 0.f;
-            }
-            sm[idx] = v;
+    // padding entries of the staging buffers (rows beyond dk that the column's threads cover, columns beyond the
+    // CTA's) are never written by the copies: zero them once
+    if (dkp > dk || a.colsp > ncols) {
+        const int pad = NV * (dkp - dk) + (a.colsp - ncols);
+        for (int i = threadIdx.x; i < 2 * TB * pad; i += blockDim.x) {
+            const int slot = i / pad, c = i - slot * pad;
+            const int which = c / (dkp - dk > 0 ? dkp - dk : 1);
+            const int at = (dkp > dk && which < NV) ? which * dkp + dk + (c - which * (dkp - dk))
+                                                    : NV * dkp + ncols + (c - NV * (dkp - dk));
+            sm[(size_t)slot * per_tok + at] = 0.f;
         }
-        __syncthreads();
-        for (int tt = 0; tt < nb; ++tt) {
-            const float* f1 = sm + (size_t)tt * per_tok;           // q or r
-            const float* f2 = f1 + dk;                             // k
-            float o;
-            if (MODE == PRISM_SCAN_DELTA) {
-                const float* vv = f2 + dk;
-                const float beta = vv[a.cols], g = vv[a.cols + 1];
-                float ks = 0.f;
+    }
+    if (MODE == PRISM_SCAN_BONUS)
+        for (int i = threadIdx.x; i < dkp; i += blockDim.x) ub[i] = i < dk ? load_param(a.u, a.u_bf16, (size_t)h * dk + i) : 0.f;
+    __syncthreads();
+
+    auto stage = [&](int b0, int buf) {
+        const int nb = min(TB, qlen - b0);
+        float* dst0 = sm + (size_t)buf * TB * per_tok;
+        const int unit = a.vec ? 4 : 1;
+        const int nk = (dk + unit - 1) / unit, nc = (ncols + unit - 1) / unit;     // pieces per vector
+        const int per = NV * nk + nc + (MODE == PRISM_SCAN_DELTA ? 2 : 0);
+        for (int idx = threadIdx.x; idx < nb * per; idx += blockDim.x) {
+            const int tt = idx / per;
+            int c = idx - tt * per;
+            const size_t t = (size_t)(s0 + b0 + tt);
+            float* dst = dst0 + (size_t)tt * per_tok;
+            if (c < NV * nk) {
+                const int which = c / nk, e = (c - which * nk) * unit;
+                const float* src;
+                if (MODE == PRISM_SCAN_DELTA) src = x + t * a.xs + (which == 0 ? a.qo : a.ko) + (size_t)kvh * dk + e;
+                else src = which == 2 ? ww + t * a.ws + (size_t)h * dk + e : x + t * a.xs + (which == 0 ? a.qo : a.ko) + (size_t)h * dk + e;
+                cp_async_f(dst + which * dkp + e, src, unit);
+            } else if ((c -= NV * nk) < nc) {
+                cp_async_f(dst + NV * dkp + c * unit, x + t * a.xs + a.vo + (size_t)h * dv + col0 + c * unit, unit);
+            } else {
+                c -= nc;                                                             // DELTA: beta, then g
+                cp_async_f(dst + NV * dkp + a.colsp + c, bg + t * 2 * a.H + (size_t)c * a.H + h, 1);
+            }
+        }
+    };
+
+    float S[R];
+    float* st = a.state + (((size_t)a.slots[seg] * a.H + h) * dv + col) * dk;
 #pragma unroll
-                for (int n = 0; n < R; ++n) {
-                    const int i = part + L * n;
-                    if (i < dk) ks += S[n] * f2[i];
+    for (int m = 0; m < Q; ++m) {
+        const int i = 4 * (part + L * m);
+        if (live && a.vec && i + 3 < dk) {
+            const float4 v = *reinterpret_cast<const float4*>(st + i);
+            S[4 * m] = v.x; S[4 * m + 1] = v.y; S[4 * m + 2] = v.z; S[4 * m + 3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) S[4 * m + j] = (live && i + j < dk) ? st[i + j] : 0.f;
+        }
+    }
+
+    stage(0, 0);
+    cp_async_commit();
+    int buf = 0;
+    for (int b0 = 0; b0 < qlen; b0 += TB, buf ^= 1) {
+        const int nb = min(TB, qlen - b0);
+        if (b0 + TB < qlen) stage(b0 + TB, buf ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        float* blk = sm + (size_t)buf * TB * per_tok;
+        if (MODE == PRISM_SCAN_BONUS) {                // the decay from its exponent, in place
+            for (int idx = threadIdx.x; idx < nb * dk; idx += blockDim.x) {
+                const int tt = idx / dk, i = idx - tt * dk;
+                float* w = blk + (size_t)tt * per_tok + 2 * dkp + i;
+                *w = expf(-expf(*w + load_param(a.w0, a.w0_bf16, (size_t)h * dk + i)));
+            }
+            __syncthreads();
+        }
+        for (int tt = 0; tt < nb; ++tt) {
+            const float* f1 = blk + (size_t)tt * per_tok;          // q or r
+            const float* f2 = f1 + dkp;                            // k
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+            if (MODE == PRISM_SCAN_DELTA) {
+                const float* vv = f2 + dkp;
+                const float beta = vv[a.colsp], g = vv[a.colsp + 1];
+                float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;        // four chains of multiply-adds side by side
+                float4 kq[Q];
+#pragma unroll
+                for (int m = 0; m < Q; ++m) {
+                    kq[m] = *reinterpret_cast<const float4*>(f2 + 4 * (part + L * m));
+                    k0 += S[4 * m] * kq[m].x;
+                    k1 += S[4 * m + 1] * kq[m].y;
+                    k2 += S[4 * m + 2] * kq[m].z;
+                    k3 += S[4 * m + 3] * kq[m].w;
                 }
+                float ks = (k0 + k1) + (k2 + k3);
                 for (int off = L >> 1; off > 0; off >>= 1) ks += __shfl_xor_sync(0xffffffffu, ks, off);
                 const float uu = beta * (vv[lc] - g * ks);
-                o = 0.f;
 #pragma unroll
-                for (int n = 0; n < R; ++n) {
-                    const int i = part + L * n;
-                    if (i < dk) {
-                        S[n] = g * S[n] + f2[i] * uu;
-                        o += S[n] * f1[i];
-                    }
+                for (int m = 0; m < Q; ++m) {
+                    const float4 qq = *reinterpret_cast<const float4*>(f1 + 4 * (part + L * m));
+                    S[4 * m] = g * S[4 * m] + kq[m].x * uu;
+                    S[4 * m + 1] = g * S[4 * m + 1] + kq[m].y * uu;
+                    S[4 * m + 2] = g * S[4 * m + 2] + kq[m].z * uu;
+                    S[4 * m + 3] = g * S[4 * m + 3] + kq[m].w * uu;
+                    o0 += S[4 * m] * qq.x;
+                    o1 += S[4 * m + 1] * qq.y;
+                    o2 += S[4 * m + 2] * qq.z;
+                    o3 += S[4 * m + 3] * qq.w;
                 }
             } else {
-                const float* wd = f2 + dk;
-                const float v = wd[dk + lc];
-                o = 0.f;
+                const float* wd = f2 + dkp;
+                const float v = wd[dkp + lc];
 #pragma unroll
-                for (int n = 0; n < R; ++n) {
-                    const int i = part + L * n;
-                    if (i < dk) {
-                        const float kv = f2[i] * v;
-                        o += f1[i] * (S[n] + ub[i] * kv);
-                        S[n] = wd[i] * S[n] + kv;
-                    }
+                for (int m = 0; m < Q; ++m) {
+                    const int i = 4 * (part + L * m);
+                    const float4 rr = *reinterpret_cast<const float4*>(f1 + i), kk = *reinterpret_cast<const float4*>(f2 + i);
+                    const float4 w4 = *reinterpret_cast<const float4*>(wd + i), u4 = *reinterpret_cast<const float4*>(ub + i);
+                    const float kv0 = kk.x * v, kv1 = kk.y * v, kv2 = kk.z * v, kv3 = kk.w * v;
+                    o0 += rr.x * (S[4 * m] + u4.x * kv0);
+                    o1 += rr.y * (S[4 * m + 1] + u4.y * kv1);
+                    o2 += rr.z * (S[4 * m + 2] + u4.z * kv2);
+                    o3 += rr.w * (S[4 * m + 3] + u4.w * kv3);
+                    S[4 * m] = w4.x * S[4 * m] + kv0;
+                    S[4 * m + 1] = w4.y * S[4 * m + 1] + kv1;
+                    S[4 * m + 2] = w4.z * S[4 * m + 2] + kv2;
+                    S[4 * m + 3] = w4.w * S[4 * m + 3] + kv3;
                 }
             }
+            float o = (o0 + o1) + (o2 + o3);
             for (int off = L >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
             if (live && part == 0) a.out[((size_t)(s0 + b0 + tt) * a.H + h) * dv + col] = o;
         }
+        __syncthreads();                               // the buffer is free for the block after the next
     }
+    cp_async_wait<0>();
     if (live) {
 #pragma unroll
-        for (int n = 0; n < R; ++n) {
-            const int i = part + L * n;
-            if (i < dk) st[i] = S[n];
+        for (int m = 0; m < Q; ++m) {
+            const int i = 4 * (part + L * m);
+            if (a.vec && i + 3 < dk) {
+                *reinterpret_cast<float4*>(st + i) = make_float4(S[4 * m], S[4 * m + 1], S[4 * m + 2], S[4 * m + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (i + j < dk) st[i + j] = S[4 * m + j];
+            }
         }
     }
 }
 
 template <int MODE, int R>
 static int launch_scan(const ScanArgs& a, int S, cudaStream_t stream) {
-    const int per_tok = (MODE == PRISM_SCAN_BONUS ? 3 : 2) * a.dk + a.cols + 2;
-    const size_t smem = ((size_t)a.TB * per_tok + (MODE == PRISM_SCAN_BONUS ? a.dk : 0)) * sizeof(float);
+    const int per_tok = (MODE == PRISM_SCAN_BONUS ? 3 : 2) * a.dkp + a.colsp + 4;
+    const size_t smem = ((size_t)2 * a.TB * per_tok + (MODE == PRISM_SCAN_BONUS ? a.dkp : 0)) * sizeof(float);
     auto kern = scan_kernel<MODE, R>;
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -343,10 +417,11 @@ PRISM_EXPORT int prism_headnorm_gate(const float* o, const float* gate, long lon
 
 // mode PRISM_SCAN_*; state [slots, H, dv, dk] float32; out [T, H, dv] float32; rep: heads per q/k head (DELTA).
 // Returns cudaErrorInvalidValue for dk > 1024.
-PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stride, int qo, int ko, int vo, const float* bg,
+PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stride, long long qo, long long ko, long long vo,
+                                      const float* bg,
                                       const float* ww, long long ww_stride, const void* w0, int w0_dtype, const void* u,
-                                      int u_dtype, float* state, const int* seg_start, const int* slots, int S, int H, int rep,
-                                      int dk, int dv, float* out, cudaStream_t stream) {
+                                      int u_dtype, float* state, const int* seg_start, const int* slots, int S, int max_q_len,
+                                      int H, int rep, int dk, int dv, float* out, cudaStream_t stream) {
     using namespace prism;
     if (S <= 0) return 0;
     if (H < 1 || rep < 1 || dk < 1 || dv < 1 || dk > 1024 || S > 65535) return (int)cudaErrorInvalidValue;
@@ -354,17 +429,34 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     a.x = x; a.xs = x_stride; a.qo = qo; a.ko = ko; a.vo = vo; a.bg = bg; a.ww = ww; a.ws = ww_stride;
     a.w0 = w0; a.w0_bf16 = w0_dtype == PRISM_DTYPE_BF16; a.u = u; a.u_bf16 = u_dtype == PRISM_DTYPE_BF16;
     a.state = state; a.seg_start = seg_start; a.slots = slots; a.out = out; a.H = H; a.rep = rep; a.dk = dk; a.dv = dv;
-    const int R = dk > 512 ? 32 : 16;
+    // A token's work is one chain: dot product, shuffles, update, dot product, shuffles.  Four threads a column
+    // keep the shuffles at two levels; their rows (up to 32 each) run as four chains of multiply-adds side by side.
+    const int R = dk <= 16 ? 4 : (dk <= 32 ? 8 : (dk <= 64 ? 16 : 32));
     int L = 1;
     while (L * R < dk) L *= 2;                          // at most 32
     a.L = L;
-    a.cols = 128 / L < dv ? 128 / L : dv;              // about 128 threads a CTA
-    const int per_tok = (mode == PRISM_SCAN_BONUS ? 3 : 2) * dk + a.cols + 2;
-    int tb = (32 * 1024 / 4) / per_tok;
-    a.TB = tb < 1 ? 1 : (tb > 16 ? 16 : tb);
-    if (mode == PRISM_SCAN_DELTA)
-        return R == 16 ? launch_scan<PRISM_SCAN_DELTA, 16>(a, S, stream) : launch_scan<PRISM_SCAN_DELTA, 32>(a, S, stream);
-    if (mode == PRISM_SCAN_BONUS)
-        return R == 16 ? launch_scan<PRISM_SCAN_BONUS, 16>(a, S, stream) : launch_scan<PRISM_SCAN_BONUS, 32>(a, S, stream);
+    a.dkp = L * R;                                     // the rows the threads of a column cover; beyond dk: zeros
+    // about 128 threads a CTA; fewer (down to one warp) while the grid would leave SMs idle: every CTA walks
+    // its tokens alone, and more of them side by side cost nothing
+    int threads = 128;
+    while (threads > 32 && (long long)H * S * ((dv + threads / L - 1) / (threads / L > 0 ? threads / L : 1)) < 296) threads /= 2;
+    int cols = threads / L < 1 ? 1 : threads / L;
+    if (cols > dv) cols = dv;
+    if (cols >= 4) cols = cols / 4 * 4;
+    a.cols = cols;
+    a.colsp = (cols + 3) / 4 * 4;
+    a.vec = dk % 4 == 0 && dv % 4 == 0 && cols % 4 == 0 && x_stride % 4 == 0 && qo % 4 == 0 && ko % 4 == 0 && vo % 4 == 0 &&
+            (uintptr_t)x % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+            (mode != PRISM_SCAN_BONUS || (ww_stride % 4 == 0 && (uintptr_t)ww % 16 == 0));
+    const int per_tok = (mode == PRISM_SCAN_BONUS ? 3 : 2) * a.dkp + a.colsp + 4;
+    int tb = (24 * 1024 / 4) / per_tok;
+    tb = tb < 1 ? 1 : (tb > 16 ? 16 : tb);
+    a.TB = tb > max_q_len ? (max_q_len < 1 ? 1 : max_q_len) : tb;      // a decode step stages one token, and CTAs are small
+#define PRISM_SCAN(M)                                                                                \
+    return R == 4 ? launch_scan<M, 4>(a, S, stream) : R == 8 ? launch_scan<M, 8>(a, S, stream)         \
+         : (R == 16 ? launch_scan<M, 16>(a, S, stream) : launch_scan<M, 32>(a, S, stream))
+    if (mode == PRISM_SCAN_DELTA) PRISM_SCAN(PRISM_SCAN_DELTA);
+    if (mode == PRISM_SCAN_BONUS) PRISM_SCAN(PRISM_SCAN_BONUS);
+#undef PRISM_SCAN
     return (int)cudaErrorInvalidValue;
 }

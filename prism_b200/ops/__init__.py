@@ -103,7 +103,7 @@ class _Sig:
     prism_state_tail = [_p, _ll, _i, _p, _i, _p, _p, _i, _p]
     prism_shift_mix = [_p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _ll, _p]
     prism_headnorm_gate = [_p, _p, _ll, _p, _i, _i, _f, _f, _i, _i, _i, _p, _i, _ll, _p]
-    prism_recurrent_scan = [_i, _p, _ll, _i, _i, _i, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _p, _p]
+    prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _i,
                              _p, _ll, _p]
@@ -1585,5 +1585,6 @@ def recurrent_scan(mode: int, x: torch.Tensor, q_off: int, k_off: int, v_off: in
     _check(lib().prism_recurrent_scan(
         int(mode), _ptr(x), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(bg), _ptr(ww),
         0 if ww is None else ww.stride(0), _ptr(w0), F32 if w0 is None else _dt(w0), _ptr(u), F32 if u is None else _dt(u),
-        _ptr(state), _ptr(ctx.seg_start), _ptr(ctx.state_slots), ctx.S, H, rep, dk, dv, _ptr(out), _stream()),
+        _ptr(state), _ptr(ctx.seg_start), _ptr(ctx.state_slots), ctx.S, int(getattr(ctx, "max_q_len", None) or T), H, rep, dk, dv,
+        _ptr(out), _stream()),
         "recurrent_scan")
