@@ -41,10 +41,11 @@ __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log
 // ---------------------------------------------------------------------------------------------------------
 __global__ void conv_unit_gates_kernel(const float* __restrict__ proj_in, long long ps, int ob, int oa,
                                        const void* __restrict__ taps, int taps_bf16, int K,
-                                       const float* __restrict__ tail, const void* __restrict__ a_log, int a_log_bf16,
+                                       const float* tail, const void* __restrict__ a_log, int a_log_bf16,
                                        const void* __restrict__ dt_bias, int dt_bf16, const int* __restrict__ tok_seg,
                                        const int* __restrict__ seg_start, const int* __restrict__ slots, int G, int H,
-                                       int dk, int dv, float unit_eps, float* __restrict__ qkv, float* __restrict__ bg) {
+                                       int dk, int dv, float unit_eps, float* __restrict__ qkv, float* __restrict__ bg,
+                                       int move_tail) {
     pdl_trigger();
     pdl_wait();
     const float* proj = pdl_fresh(proj_in);
@@ -52,7 +53,7 @@ __global__ void conv_unit_gates_kernel(const float* __restrict__ proj_in, long l
     const int t = blockIdx.x, seg = tok_seg[t];
     const int i = t - seg_start[seg];                  // place of the token in its segment
     const int C = 2 * G * dk + H * dv;
-    const float* tl = tail + (size_t)slots[seg] * (K - 1) * C;
+    float* tl = const_cast<float*>(tail) + (size_t)slots[seg] * (K - 1) * C;
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
         float acc = 0.f;
         for (int j = K - 1; j >= 0; --j) {             // lag j: the input j tokens back; oldest first
@@ -61,6 +62,12 @@ __global__ void conv_unit_gates_kernel(const float* __restrict__ proj_in, long l
             acc += load_param(taps, taps_bf16, (size_t)c * K + (K - 1 - j)) * x;
         }
         y[c] = silu_f(acc);
+        // a step of single tokens: this CTA is the only reader of its request's tail, and a thread the only one of
+        // its channel, so it moves the tail up by this token itself (no second launch)
+        if (move_tail && K > 1) {
+            for (int r = 0; r + 2 < K; ++r) tl[(size_t)r * C + c] = tl[(size_t)(r + 1) * C + c];
+            tl[(size_t)(K - 2) * C + c] = proj[(size_t)t * ps + c];
+        }
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -100,19 +107,21 @@ __global__ void state_tail_kernel(const float* __restrict__ src_in, long long ss
 
 // out[s][t][c] = x[t][c] + (x_prev[t][c] - x[t][c]) mu[s][c],  s < n;  x_prev of a segment's first token is prev[slot].
 template <typename T>
-__global__ void shift_mix_kernel(const float* __restrict__ x_in, int D, const float* __restrict__ prev,
+__global__ void shift_mix_kernel(const float* __restrict__ x_in, int D, const float* prev,
                                  const void* __restrict__ mu, int mu_bf16, int n, const int* __restrict__ tok_seg,
                                  const int* __restrict__ seg_start, const int* __restrict__ slots, T* __restrict__ out,
-                                 long long out_plane) {
+                                 long long out_plane, int keep_prev) {
     pdl_trigger();
     pdl_wait();
     const float* x = pdl_fresh(x_in);
     const int t = blockIdx.x, seg = tok_seg[t];
-    const float* xp = t > seg_start[seg] ? x + (size_t)(t - 1) * D : prev + (size_t)slots[seg] * D;
+    float* own = const_cast<float*>(prev) + (size_t)slots[seg] * D;
+    const float* xp = t > seg_start[seg] ? x + (size_t)(t - 1) * D : own;
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
         const float a = x[(size_t)t * D + c], d = xp[c] - a;
         for (int s = 0; s < n; ++s)
             out[(size_t)s * out_plane + (size_t)t * D + c] = from_float<T>(a + d * load_param(mu, mu_bf16, (size_t)s * D + c));
+        if (keep_prev) own[c] = a;       // a step of single tokens: this token is its request's previous one from now on
     }
 }
 
@@ -190,10 +199,13 @@ __global__ void scan_kernel(const ScanArgs a) {
     const int s0 = a.seg_start[seg], qlen = a.seg_start[seg + 1] - s0;
     const int L = a.L, dk = a.dk, dkp = a.dkp, dv = a.dv, TB = a.TB;
     const int ncols = min(a.cols, dv - col0);
-    // the block is a whole number of warps: threads beyond the CTA's columns run along (they take part in the
-    // shuffles) and neither load nor store
+    // The CTA's last warp brings the step's vectors in (and, for the decayed sum, turns the decay's exponent into
+    // the decay); the warps before it own the state.  Their threads beyond the CTA's columns run along (they
+    // take part in the shuffles) and neither load nor store.
+    const int CT = blockDim.x - 32;
+    const bool producer = (int)threadIdx.x >= CT;
     const int part = threadIdx.x % L;
-    const bool live = (int)threadIdx.x / L < ncols;
+    const bool live = !producer && (int)threadIdx.x / L < ncols;
     const int lc = live ? threadIdx.x / L : 0, col = col0 + lc;
     const int kvh = h / a.rep;                         // DELTA: the q/k head this head uses
     // shared, per token of a block:  first[dkp] (q or r) | second[dkp] (k) | third[dkp] (BONUS: w) | v[colsp] | 4 scalars
@@ -219,72 +231,76 @@ __global__ void scan_kernel(const ScanArgs a) {
         for (int i = threadIdx.x; i < dkp; i += blockDim.x) ub[i] = i < dk ? load_param(a.u, a.u_bf16, (size_t)h * dk + i) : 0.f;
     __syncthreads();
 
+    // the producer warp: block b0 of the segment's tokens into buffer `buf`, complete when it returns
     auto stage = [&](int b0, int buf) {
+        const int lane = threadIdx.x - CT;
         const int nb = min(TB, qlen - b0);
         float* dst0 = sm + (size_t)buf * TB * per_tok;
         const int unit = a.vec ? 4 : 1;
         const int nk = (dk + unit - 1) / unit, nc = (ncols + unit - 1) / unit;     // pieces per vector
-        const int per = NV * nk + nc + (MODE == PRISM_SCAN_DELTA ? 2 : 0);
-        for (int idx = threadIdx.x; idx < nb * per; idx += blockDim.x) {
-            const int tt = idx / per;
-            int c = idx - tt * per;
+        const size_t head_q = (size_t)(MODE == PRISM_SCAN_DELTA ? kvh : h) * dk;
+        for (int tt = 0; tt < nb; ++tt) {
             const size_t t = (size_t)(s0 + b0 + tt);
+            const float* xr = x + t * a.xs;
             float* dst = dst0 + (size_t)tt * per_tok;
-            if (c < NV * nk) {
-                const int which = c / nk, e = (c - which * nk) * unit;
-                const float* src;
-                if (MODE == PRISM_SCAN_DELTA) src = x + t * a.xs + (which == 0 ? a.qo : a.ko) + (size_t)kvh * dk + e;
-                else src = which == 2 ? ww + t * a.ws + (size_t)h * dk + e : x + t * a.xs + (which == 0 ? a.qo : a.ko) + (size_t)h * dk + e;
-                cp_async_f(dst + which * dkp + e, src, unit);
-            } else if ((c -= NV * nk) < nc) {
-                cp_async_f(dst + NV * dkp + c * unit, x + t * a.xs + a.vo + (size_t)h * dv + col0 + c * unit, unit);
-            } else {
-                c -= nc;                                                             // DELTA: beta, then g
-                cp_async_f(dst + NV * dkp + a.colsp + c, bg + t * 2 * a.H + (size_t)c * a.H + h, 1);
+            for (int c = lane; c < nk; c += 32) {
+                cp_async_f(dst + c * unit, xr + a.qo + head_q + c * unit, unit);
+                cp_async_f(dst + dkp + c * unit, xr + a.ko + head_q + c * unit, unit);
+                if (MODE == PRISM_SCAN_BONUS) cp_async_f(dst + 2 * dkp + c * unit, ww + t * a.ws + (size_t)h * dk + c * unit, unit);
+            }
+            for (int c = lane; c < nc; c += 32)
+                cp_async_f(dst + NV * dkp + c * unit, xr + a.vo + (size_t)h * dv + col0 + c * unit, unit);
+            if (MODE == PRISM_SCAN_DELTA && lane < 2)                                // beta, then g
+                cp_async_f(dst + NV * dkp + a.colsp + lane, bg + t * 2 * a.H + (size_t)lane * a.H + h, 1);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        __syncwarp();
+        if (MODE == PRISM_SCAN_BONUS) {                // the decay from its exponent, in place
+            for (int idx = lane; idx < nb * dk; idx += 32) {
+                const int tt = idx / dk, i = idx - tt * dk;
+                float* w = dst0 + (size_t)tt * per_tok + 2 * dkp + i;
+                *w = expf(-expf(*w + load_param(a.w0, a.w0_bf16, (size_t)h * dk + i)));
             }
         }
     };
 
     float S[R];
     float* st = a.state + (((size_t)a.slots[seg] * a.H + h) * dv + col) * dk;
+    if (producer) {
+        stage(0, 0);
+    } else {
 #pragma unroll
-    for (int m = 0; m < Q; ++m) {
-        const int i = 4 * (part + L * m);
-        if (live && a.vec && i + 3 < dk) {
-            const float4 v = *reinterpret_cast<const float4*>(st + i);
-            S[4 * m] = v.x; S[4 * m + 1] = v.y; S[4 * m + 2] = v.z; S[4 * m + 3] = v.w;
-        } else {
+        for (int m = 0; m < Q; ++m) {
+            const int i = 4 * (part + L * m);
+            if (live && a.vec && i + 3 < dk) {
+                const float4 v = *reinterpret_cast<const float4*>(st + i);
+                S[4 * m] = v.x; S[4 * m + 1] = v.y; S[4 * m + 2] = v.z; S[4 * m + 3] = v.w;
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) S[4 * m + j] = (live && i + j < dk) ? st[i + j] : 0.f;
+                for (int j = 0; j < 4; ++j) S[4 * m + j] = (live && i + j < dk) ? st[i + j] : 0.f;
+            }
         }
     }
+    __syncthreads();
 
-    stage(0, 0);
-    cp_async_commit();
     int buf = 0;
     for (int b0 = 0; b0 < qlen; b0 += TB, buf ^= 1) {
         const int nb = min(TB, qlen - b0);
-        if (b0 + TB < qlen) stage(b0 + TB, buf ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        float* blk = sm + (size_t)buf * TB * per_tok;
-        if (MODE == PRISM_SCAN_BONUS) {                // the decay from its exponent, in place
-            for (int idx = threadIdx.x; idx < nb * dk; idx += blockDim.x) {
-                const int tt = idx / dk, i = idx - tt * dk;
-                float* w = blk + (size_t)tt * per_tok + 2 * dkp + i;
-                *w = expf(-expf(*w + load_param(a.w0, a.w0_bf16, (size_t)h * dk + i)));
-            }
+        if (producer) {
+            if (b0 + TB < qlen) stage(b0 + TB, buf ^ 1);
             __syncthreads();
+            continue;
         }
+        const float* blk = sm + (size_t)buf * TB * per_tok;
         for (int tt = 0; tt < nb; ++tt) {
             const float* f1 = blk + (size_t)tt * per_tok;          // q or r
             const float* f2 = f1 + dkp;                            // k
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;         // four chains of multiply-adds side by side
             if (MODE == PRISM_SCAN_DELTA) {
                 const float* vv = f2 + dkp;
                 const float beta = vv[a.colsp], g = vv[a.colsp + 1];
-                float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;        // four chains of multiply-adds side by side
+                float k0 = 0.f, k1 = 0.f, k2 = 0.f, k3 = 0.f;
                 float4 kq[Q];
 #pragma unroll
                 for (int m = 0; m < Q; ++m) {
@@ -332,9 +348,8 @@ __global__ void scan_kernel(const ScanArgs a) {
             for (int off = L >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
             if (live && part == 0) a.out[((size_t)(s0 + b0 + tt) * a.H + h) * dv + col] = o;
         }
-        __syncthreads();                               // the buffer is free for the block after the next
+        __syncthreads();                               // the next block has landed, and this buffer is free
     }
-    cp_async_wait<0>();
     if (live) {
 #pragma unroll
         for (int m = 0; m < Q; ++m) {
@@ -358,7 +373,7 @@ static int launch_scan(const ScanArgs& a, int S, cudaStream_t stream) {
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(a.H, S, (a.dv + a.cols - 1) / a.cols);
-    return (int)launch_kernel(kern, grid, dim3((a.cols * a.L + 31) / 32 * 32), smem, stream, a);
+    return (int)launch_kernel(kern, grid, dim3((a.cols * a.L + 31) / 32 * 32 + 32), smem, stream, a);      // + the producer warp
 }
 
 }  // namespace prism
@@ -366,7 +381,8 @@ static int launch_scan(const ScanArgs& a, int S, cudaStream_t stream) {
 PRISM_EXPORT int prism_conv_unit_gates(const float* proj, long long ps, int ob, int oa, const void* taps, int taps_dtype,
                                        int K, const float* tail, const void* a_log, int a_log_dtype, const void* dt_bias,
                                        int dt_dtype, const int* tok_seg, const int* seg_start, const int* slots, int T, int G,
-                                       int H, int dk, int dv, float unit_eps, float* qkv, float* bg, cudaStream_t stream) {
+                                       int H, int dk, int dv, float unit_eps, float* qkv, float* bg, int move_tail,
+                                       cudaStream_t stream) {
     if (T <= 0) return 0;
     if (K < 1 || G < 1 || H < 1 || dk < 1 || dv < 1) return (int)cudaErrorInvalidValue;
     const int C = 2 * G * dk + H * dv;
@@ -374,9 +390,11 @@ PRISM_EXPORT int prism_conv_unit_gates(const float* proj, long long ps, int ob, 
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     auto kern = prism::conv_unit_gates_kernel;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return (int)prism::launch_kernel(kern, dim3(T), dim3(C >= 2048 ? 256 : 128), smem, stream, proj, ps, ob, oa, taps,
+    const int threads = C >= 2048 ? 1024 : (C >= 512 ? 256 : 128);          // a few channels a thread: their loads are one chain each
+    return (int)prism::launch_kernel(kern, dim3(T), dim3(threads), smem, stream, proj, ps, ob, oa, taps,
                                      taps_dtype == PRISM_DTYPE_BF16, K, tail, a_log, a_log_dtype == PRISM_DTYPE_BF16, dt_bias,
-                                     dt_dtype == PRISM_DTYPE_BF16, tok_seg, seg_start, slots, G, H, dk, dv, unit_eps, qkv, bg);
+                                     dt_dtype == PRISM_DTYPE_BF16, tok_seg, seg_start, slots, G, H, dk, dv, unit_eps, qkv, bg,
+                                     move_tail);
 }
 
 PRISM_EXPORT int prism_state_tail(const float* src, long long src_stride, int width, float* tail, int rows,
@@ -388,15 +406,15 @@ PRISM_EXPORT int prism_state_tail(const float* src, long long src_stride, int wi
 
 PRISM_EXPORT int prism_shift_mix(const float* x, int D, const float* prev, const void* mu, int mu_dtype, int n,
                                  const int* tok_seg, const int* seg_start, const int* slots, int T, void* out, int out_dtype,
-                                 long long out_plane, cudaStream_t stream) {
+                                 long long out_plane, int keep_prev, cudaStream_t stream) {
     if (T <= 0 || n <= 0) return 0;
-    const int threads = D >= 1024 ? 256 : 128;
+    const int threads = D >= 2048 ? 1024 : (D >= 512 ? 256 : 128);
     const int mb = mu_dtype == PRISM_DTYPE_BF16;
     if (out_dtype == PRISM_DTYPE_BF16)
         return (int)prism::launch_kernel(prism::shift_mix_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, x, D, prev, mu,
-                                         mb, n, tok_seg, seg_start, slots, (__nv_bfloat16*)out, out_plane);
+                                         mb, n, tok_seg, seg_start, slots, (__nv_bfloat16*)out, out_plane, keep_prev);
     return (int)prism::launch_kernel(prism::shift_mix_kernel<float>, dim3(T), dim3(threads), 0, stream, x, D, prev, mu, mb, n,
-                                     tok_seg, seg_start, slots, (float*)out, out_plane);
+                                     tok_seg, seg_start, slots, (float*)out, out_plane, keep_prev);
 }
 
 PRISM_EXPORT int prism_headnorm_gate(const float* o, const float* gate, long long gate_stride, const void* weight,
@@ -429,17 +447,16 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     a.x = x; a.xs = x_stride; a.qo = qo; a.ko = ko; a.vo = vo; a.bg = bg; a.ww = ww; a.ws = ww_stride;
     a.w0 = w0; a.w0_bf16 = w0_dtype == PRISM_DTYPE_BF16; a.u = u; a.u_bf16 = u_dtype == PRISM_DTYPE_BF16;
     a.state = state; a.seg_start = seg_start; a.slots = slots; a.out = out; a.H = H; a.rep = rep; a.dk = dk; a.dv = dv;
-    // A token's work is one chain: dot product, shuffles, update, dot product, shuffles.  Four threads a column
-    // keep the shuffles at two levels; their rows (up to 32 each) run as four chains of multiply-adds side by side.
-    const int R = dk <= 16 ? 4 : (dk <= 32 ? 8 : (dk <= 64 ? 16 : 32));
+    // A token's work is one chain (dot product, shuffles, update, dot product, shuffles), so a CTA is latency
+    // bound: eight threads a column, four warps of them side by side, and as many CTAs as there are column blocks.
+    const int R = dk <= 32 ? 4 : (dk <= 64 ? 8 : (dk <= 128 ? 16 : 32));
     int L = 1;
     while (L * R < dk) L *= 2;                          // at most 32
     a.L = L;
     a.dkp = L * R;                                     // the rows the threads of a column cover; beyond dk: zeros
-    // about 128 threads a CTA; fewer (down to one warp) while the grid would leave SMs idle: every CTA walks
-    // its tokens alone, and more of them side by side cost nothing
+    // 128 threads a CTA beside the producer warp; fewer (down to one warp) while the grid would leave SMs idle
     int threads = 128;
-    while (threads > 32 && (long long)H * S * ((dv + threads / L - 1) / (threads / L > 0 ? threads / L : 1)) < 296) threads /= 2;
+    while (threads > 32 && (long long)H * S * ((dv + threads / L - 1) / (threads / L)) < 148) threads /= 2;
     int cols = threads / L < 1 ? 1 : threads / L;
     if (cols > dv) cols = dv;
     if (cols >= 4) cols = cols / 4 * 4;

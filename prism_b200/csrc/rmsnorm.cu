@@ -131,6 +131,70 @@ __global__ void scale_add_rmsnorm_kernel(float* __restrict__ x, float alpha, con
     }
 }
 
+// Vector version for H % 8 == 0 and H <= 8 * 1024 * ITERS: a thread keeps its 8 * ITERS values in registers, the
+// partial sums' loads are independent of one another (four in flight per pass), the weight is read before the wait.
+template <typename TD, typename TO, int ITERS>
+__global__ void __launch_bounds__(1024) scale_add_rmsnorm_vec_kernel(float* __restrict__ x, float alpha, const TD* __restrict__ delta_in,
+                                                                     int nsplit, size_t split_stride, const void* __restrict__ weight,
+                                                                     int weight_bf16, float eps, TO* __restrict__ copy, int H) {
+    pdl_trigger();
+    float w[ITERS][8];
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (threadIdx.x + it * blockDim.x) * 8;
+        if (c < H) load_param8(weight, weight_bf16, c, w[it]);
+    }
+    pdl_wait();
+    const TD* delta = pdl_fresh(delta_in);
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    float* row = x + (size_t)r * H;
+    float v[ITERS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (threadIdx.x + it * blockDim.x) * 8;
+        if (c < H) {
+            load8(row + c, v[it]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[it][k] *= alpha;
+            if (delta != nullptr) {
+                const TD* d0 = delta + (size_t)r * H + c;
+                int s = 0;
+                for (; s + 4 <= nsplit; s += 4) {
+                    float d[4][8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) load8(d0 + (size_t)(s + j) * split_stride, d[j]);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) v[it][k] += d[j][k];
+                }
+                for (; s < nsplit; ++s) {
+                    float d[8];
+                    load8(d0 + (size_t)s * split_stride, d);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) v[it][k] += d[k];
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss += v[it][k] * v[it][k];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+        const int c = (threadIdx.x + it * blockDim.x) * 8;
+        if (c < H) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[it][k] *= inv * w[it][k];
+            store8(row + c, v[it]);
+            if (copy != nullptr) store8(copy + (size_t)r * H + c, v[it]);
+        }
+    }
+}
+
 }  // namespace prism
 
 // x float32 [rows, H] in place; delta (null: none) [nsplit, rows, H] of delta_dtype; copy (null: none) [rows, H] of
@@ -140,10 +204,22 @@ PRISM_EXPORT int prism_scale_add_rmsnorm(float* x, float alpha, const void* delt
                                          void* copy, int copy_dtype, int rows, int H, cudaStream_t stream) {
     if (rows <= 0) return 0;
     const int wb = weight_dtype == PRISM_DTYPE_BF16;
-    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    const int chunks = H / 8;
+    const bool vec = H % 8 == 0 && chunks <= 2048 && split_stride % 8 == 0 && (uintptr_t)x % 32 == 0 &&
+                     (uintptr_t)delta % 32 == 0 && (uintptr_t)copy % 32 == 0 && (uintptr_t)weight % 32 == 0;
+    const int iters = chunks > 1024 ? 2 : 1;
+    const int threads = vec ? ((chunks + iters - 1) / iters + 31) / 32 * 32 : (H >= 4096 ? 512 : (H >= 1024 ? 256 : 128));
 #define LAUNCH(TD, TO)                                                                                              \
-    return (int)prism::launch_kernel(prism::scale_add_rmsnorm_kernel<TD, TO>, dim3(rows), dim3(threads), 0, stream, x,  \
-                                     alpha, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, (TO*)copy, H)
+    do {                                                                                                            \
+        if (vec && iters == 1)                                                                                      \
+            return (int)prism::launch_kernel(prism::scale_add_rmsnorm_vec_kernel<TD, TO, 1>, dim3(rows), dim3(threads), 0, stream, \
+                                             x, alpha, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, (TO*)copy, H); \
+        if (vec)                                                                                                    \
+            return (int)prism::launch_kernel(prism::scale_add_rmsnorm_vec_kernel<TD, TO, 2>, dim3(rows), dim3(threads), 0, stream, \
+                                             x, alpha, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, (TO*)copy, H); \
+        return (int)prism::launch_kernel(prism::scale_add_rmsnorm_kernel<TD, TO>, dim3(rows), dim3(threads), 0, stream, x,  \
+                                         alpha, (const TD*)delta, nsplit, (size_t)split_stride, weight, wb, eps, (TO*)copy, H); \
+    } while (0)
     if (delta_dtype == PRISM_DTYPE_BF16) {
         if (copy_dtype == PRISM_DTYPE_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
         LAUNCH(__nv_bfloat16, float);

@@ -99,9 +99,9 @@ class _Sig:
     prism_gated_product = [_p, _ll, _p, _ll, _p, _ll, _i, _i, _i, _i, _f, _p]
     prism_qk_norm_rope_store = [_p, _p, _p, _ll, _p, _i, _p, _i, _f, _p, _i, _p, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i,
                                 _i, _i, _i, _i, _p, _p]
-    prism_conv_unit_gates = [_p, _ll, _i, _i, _p, _i, _i, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _p]
+    prism_conv_unit_gates = [_p, _ll, _i, _i, _p, _i, _i, _p, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _f, _p, _p, _i, _p]
     prism_state_tail = [_p, _ll, _i, _p, _i, _p, _p, _i, _p]
-    prism_shift_mix = [_p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _ll, _p]
+    prism_shift_mix = [_p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _ll, _i, _p]
     prism_headnorm_gate = [_p, _p, _ll, _p, _i, _i, _f, _f, _i, _i, _i, _p, _i, _ll, _p]
     prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
@@ -1503,12 +1503,13 @@ def qk_norm_rope_store(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_weig
 
 def conv_unit_gates(proj: torch.Tensor, b_off: int, a_off: int, taps: torch.Tensor, tail: torch.Tensor,
                     a_log: torch.Tensor, dt_bias: torch.Tensor, ctx, G: int, H: int, dk: int, dv: int, unit_eps: float,
-                    qkv: torch.Tensor, bg: torch.Tensor):
+                    qkv: torch.Tensor, bg: torch.Tensor, move_tail: bool = False):
     """The input side of the gated delta rule from the float32 projection rows ``proj`` (columns ``[0, C)``: the q
     | k | v channels, ``C = 2 G dk + H dv``; ``b_off``/``a_off``: first column of the beta / decay projections):
     short causal convolution over time with ``taps [C, K]`` (the ``K - 1`` inputs before the step in ``tail
     [slots, K - 1, C]``) and silu; q and k heads made unit vectors (q also times ``dk^-1/2``) into ``qkv [T, C]``;
-    ``bg [T, 2 H]`` = sigmoid(b) | exp(-exp(a_log) softplus(a + dt_bias))."""
+    ``bg [T, 2 H]`` = sigmoid(b) | exp(-exp(a_log) softplus(a + dt_bias)).  ``move_tail``: every request of the step
+    brings one token, and the kernel moves the tail up by it itself (else ``state_tail`` follows)."""
     _cuda(proj, taps, tail, a_log, dt_bias, qkv, bg)
     T = proj.shape[0]
     C, K = taps.shape
@@ -1519,7 +1520,7 @@ def conv_unit_gates(proj: torch.Tensor, b_off: int, a_off: int, taps: torch.Tens
     _check(lib().prism_conv_unit_gates(_ptr(proj), proj.stride(0), int(b_off), int(a_off), _ptr(taps), _dt(taps), K,
                                        _ptr(tail), _ptr(a_log), _dt(a_log), _ptr(dt_bias), _dt(dt_bias), _ptr(ctx.tok_seg),
                                        _ptr(ctx.seg_start), _ptr(ctx.state_slots), T, G, H, dk, dv, float(unit_eps),
-                                       _ptr(qkv), _ptr(bg), _stream()), "conv_unit_gates")
+                                       _ptr(qkv), _ptr(bg), 1 if move_tail else 0, _stream()), "conv_unit_gates")
 
 
 def state_tail(src: torch.Tensor, tail: torch.Tensor, ctx):
@@ -1536,16 +1537,19 @@ def state_tail(src: torch.Tensor, tail: torch.Tensor, ctx):
                                   _ptr(ctx.state_slots), ctx.S, _stream()), "state_tail")
 
 
-def shift_mix(x: torch.Tensor, prev: torch.Tensor, mu: torch.Tensor, ctx, out: torch.Tensor):
+def shift_mix(x: torch.Tensor, prev: torch.Tensor, mu: torch.Tensor, ctx, out: torch.Tensor, keep_prev: bool = False):
     """``out[s] = x + (x_prev - x) * mu[s]`` for ``mu [n, D]``; ``x [T, D]`` float32, ``x_prev`` the row before in
-    the same request (``prev [slots, 1, D]`` for a step's first token); ``out [n, T, D]`` in the compute dtype."""
+    the same request (``prev [slots, 1, D]`` for a step's first token); ``out [n, T, D]`` in the compute dtype.
+    ``keep_prev``: every request of the step brings one token, and the kernel leaves it in ``prev`` itself (else
+    ``state_tail`` follows)."""
     _cuda(x, prev, mu, out)
     T, D = x.shape
     n = mu.shape[0]
     assert x.dtype == torch.float32 and x.is_contiguous() and prev.dtype == torch.float32 and prev.is_contiguous()
     assert prev[0].numel() == D and mu.shape == (n, D) and mu.is_contiguous() and out.shape == (n, T, D) and out.is_contiguous()
     _check(lib().prism_shift_mix(_ptr(x), D, _ptr(prev), _ptr(mu), _dt(mu), n, _ptr(ctx.tok_seg), _ptr(ctx.seg_start),
-                                 _ptr(ctx.state_slots), T, _ptr(out), _dt(out), T * D, _stream()), "shift_mix")
+                                 _ptr(ctx.state_slots), T, _ptr(out), _dt(out), T * D, 1 if keep_prev else 0, _stream()),
+           "shift_mix")
 
 
 def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, scale: float, out: torch.Tensor):

@@ -102,9 +102,11 @@ class GatedDeltaMixer(Mixer):
             proj = ops.linear(x, self.w["in_w"], None, out_dtype=torch.float32)
         qkv = ctx.alloc((T, self.C), torch.float32)
         bg = ctx.alloc((T, 2 * H), torch.float32)
+        single = ctx.decode_only          # one token per request: the kernel that reads the tail also moves it up
         ops.conv_unit_gates(proj, self.b_off, self.a_off, self.w["taps"], tail.state, self.w["A_log"], self.w["dt_bias"],
-                            ctx, G, H, dk, dv, self.unit_eps, qkv, bg)
-        ops.state_tail(proj, tail.state, ctx)
+                            ctx, G, H, dk, dv, self.unit_eps, qkv, bg, move_tail=single)
+        if not single:
+            ops.state_tail(proj, tail.state, ctx)
         o = ctx.alloc((T, H, dv), torch.float32)
         ops.recurrent_scan(ops.SCAN_DELTA, qkv, 0, G * dk, 2 * G * dk, state.state, ctx, H, H // G, dk, dv, o, bg=bg)
         ops.headnorm_gate(o, proj[:, self.g_off:self.g_off + H * dv], self.w["norm"], self.eps, self.out_scale, out)
@@ -168,8 +170,9 @@ class WKVMixer(Mixer):
         if x.dtype != torch.float32:
             x = x.float()
         mixes = ctx.alloc((5, T, W), ctx.dtype)
-        ops.shift_mix(x, prev.state, self.mu, ctx, mixes)
-        ops.state_tail(x, prev.state, ctx)
+        ops.shift_mix(x, prev.state, self.mu, ctx, mixes, keep_prev=ctx.decode_only)
+        if not ctx.decode_only:
+            ops.state_tail(x, prev.state, ctx)
         proj = ctx.alloc((4, T, A), torch.float32)             # r, k, v, g: each from its own mix, one matrix each
         for i in range(4):
             ops.linear(mixes[i], self.w["rkvg_w"][i * A:(i + 1) * A], None, out=proj[i])

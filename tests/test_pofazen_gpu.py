@@ -320,6 +320,20 @@ def test_convolution_with_its_tail_unit_vectors_and_gates(G, H, dk, dv, K):
     if K > 1:
         assert float((tail[1].cpu() - proj[n - (K - 1):, :C]).abs().max()) == 0.0
         assert float(tail[0].abs().max()) == 0.0 and float(tail[2].abs().max()) == 0.0
+    # token by token, the kernel moving the tail up itself (two requests side by side, the second one step behind)
+    tail.zero_()
+    got2 = torch.empty(n, C)
+    for a in range(n + 1):
+        rows = [r for r in (a, a - 1) if 0 <= r < n]
+        ctx = step_ctx([1] * len(rows), [2 if r == a else 0 for r in rows])
+        qkv, bg = torch.empty(len(rows), C, device=DEV), torch.empty(len(rows), 2 * H, device=DEV)
+        ops.conv_unit_gates(pd[rows], C, C + H, taps.to(DEV), tail, a_log.to(DEV), dt.to(DEV), ctx, G, H, dk, dv, 1e-6, qkv, bg,
+                            move_tail=True)
+        if a < n:
+            got2[a] = qkv[0].cpu()
+        if a >= 1:
+            assert float((qkv[-1].cpu() - ref[a - 1]).abs().max()) <= 1e-5
+    assert float((got2 - ref).abs().max()) <= 1e-5
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -354,6 +368,14 @@ def test_small_kernels(dtype):
     assert float((mixes.float().cpu() - ref).abs().max()) <= tol
     ops.state_tail(xs.to(DEV), pd, ctx)
     assert torch.equal(pd[2, 0].cpu(), xs[3]) and torch.equal(pd[0, 0].cpu(), xs[5]) and torch.equal(pd[1].cpu(), prev[1])
+    # single tokens: the mix kernel keeps each token as its request's previous one itself
+    pd = prev.to(DEV)
+    ctx1 = step_ctx([1, 1], [1, 0])
+    m1 = torch.empty(5, 2, 20, dtype=dtype, device=DEV)
+    ops.shift_mix(xs[:2].to(DEV), pd, mu.to(DEV), ctx1, m1, keep_prev=True)
+    ref1 = xs[None, :2] + (torch.cat([prev[1], prev[0]]) - xs[:2])[None] * mu[:, None]
+    assert float((m1.float().cpu() - ref1).abs().max()) <= tol
+    assert torch.equal(pd[1, 0].cpu(), xs[0]) and torch.equal(pd[0, 0].cpu(), xs[1]) and torch.equal(pd[2].cpu(), prev[2])
     # head norm with one weight for all heads and with a weight per head, gate, constant
     o, gt = torch.randn(5, 3, 14, generator=g), torch.randn(5, 42, generator=g)
     for wt in (torch.randn(14, generator=g), torch.randn(42, generator=g)):
