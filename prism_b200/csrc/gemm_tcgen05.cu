@@ -50,7 +50,8 @@ template <int NTOK, int EPI>
 __global__ void __launch_bounds__(THREADS)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  const void* __restrict__ bias, int bias_bf16, void* __restrict__ y, int ldy, int M, int N, int K,
-                 int kblocks_per_split, int pair_offset, float* __restrict__ ws, int* __restrict__ counters, int* err) {
+                 int kblocks_per_split, int pair_offset, float* __restrict__ ws, int* __restrict__ counters, int* err,
+                 int group_rows, int group_tokens) {
     using C = Cfg<NTOK, EPI>;
     constexpr int W_TILES = C::W_TILES;
     constexpr int STAGES = C::STAGES;
@@ -65,6 +66,11 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * TILE_M;                    // first weight row (output feature) of this tile
+    // Grouped inputs: the weight rows [g group_rows, (g + 1) group_rows) are applied to the tokens' rows
+    // [g group_tokens, g group_tokens + M) of x (projections of the same tokens that each read a mix of their own).
+    // group_rows is a multiple of the tile, so a tile has one group; the rows a tile loads beyond its M tokens
+    // (the next group's, or none) feed accumulator columns that are never stored.
+    const int x_row0 = group_rows > 0 ? (m0 / group_rows) * group_tokens : 0;
     const int total_kb = (K + TILE_K - 1) / TILE_K;
     const int kb0 = blockIdx.y * kblocks_per_split;
     const int kb1 = min(total_kb, kb0 + kblocks_per_split);
@@ -104,7 +110,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             pdl_wait();
             for (int i = 0; i < pre; ++i)
                 tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + W_TILES * TILE_M * TILE_K * 2, &map_x, &full_bar[i],
-                            (kb0 + i) * TILE_K, 0);
+                            (kb0 + i) * TILE_K, x_row0);
             issued = pre;
             for (int i = pre; i < nkb; ++i) {
                 const int s = i % STAGES;
@@ -115,7 +121,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
                 for (int w = 0; w < W_TILES; ++w)
                     tma_load_2d(st + w * TILE_M * TILE_K * 2, &map_w, &full_bar[s], kc, m0 + w * pair_offset);
-                tma_load_2d(st + W_TILES * TILE_M * TILE_K * 2, &map_x, &full_bar[s], kc, 0);
+                tma_load_2d(st + W_TILES * TILE_M * TILE_K * 2, &map_x, &full_bar[s], kc, x_row0);
                 issued = i + 1;
             }
             pdl_trigger_gemm();     // all of this CTA's loads are on their way: the next kernel may start its prologue
@@ -232,12 +238,13 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 template <int NTOK, int EPI>
 int launch(const void* W, int ldw, long long w_rows, const void* x, int ldx, const void* bias, int bias_bf16, void* y,
            int ldy, int M, int N, int K, int ksplit, int pair_offset, float* ws, int* counters, int* err,
-           cudaStream_t stream) {
+           int group_rows, int group_tokens, cudaStream_t stream) {
     using C = Cfg<NTOK, EPI>;
     CUtensorMap mw, mx;
     int rc = make_map(&mw, W, w_rows, K, ldw, TILE_M);
     if (rc) return rc;
-    rc = make_map(&mx, x, M, K, ldx, NTOK);
+    const int groups = group_rows > 0 ? (N + group_rows - 1) / group_rows : 1;
+    rc = make_map(&mx, x, (long long)(groups - 1) * group_tokens + M, K, ldx, NTOK);
     if (rc) return rc;
     const int total_kb = (K + TILE_K - 1) / TILE_K;
     const int per = (total_kb + ksplit - 1) / ksplit;
@@ -245,7 +252,7 @@ int launch(const void* W, int ldw, long long w_rows, const void* x, int ldx, con
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM);
     dim3 grid((N + TILE_M - 1) / TILE_M, ksplit);
     return (int)launch_kernel(kern, grid, dim3(THREADS), C::SMEM, stream, mw, mx, bias, bias_bf16, y, ldy, M, N, K, per,
-                              pair_offset, ws, counters, err);
+                              pair_offset, ws, counters, err, group_rows, group_tokens);
 }
 
 }  // namespace tc
@@ -267,11 +274,15 @@ PRISM_EXPORT int prism_gemm_tcgen05_supported(int M, int N, int K) {
 // ksplit > 1 with epi 0 or 1 needs a workspace `ws` of ksplit * M * N floats and `counters`, one int per
 // 128-row tile of N, zero before the first launch (the kernel leaves them zero); the last CTA of each
 // tile adds the partial sums in split order, so the result does not depend on timing.  Not with epi 2.
+// group_rows > 0 (a multiple of 128): x holds one [M, K] block of rows per group of group_rows weight rows,
+// group_tokens rows apart, and every group of output features reads its own block.
 PRISM_EXPORT int prism_gemm_tcgen05(const void* W, int ldw, const void* x, int ldx, const void* bias, int bias_dtype,
                                     void* y, int ldy, int M, int N, int K, int epi, int ksplit, float* ws,
-                                    int* counters, int* err, cudaStream_t stream) {
+                                    int* counters, int* err, int group_rows, int group_tokens, cudaStream_t stream) {
     using namespace prism::tc;
     if (M <= 0 || N <= 0) return 0;
+    if (group_rows < 0 || group_rows % 128 || (group_rows > 0 && (group_tokens < M || epi == EPI_SWIGLU)))
+        return (int)cudaErrorInvalidValue;
     if (!prism_gemm_tcgen05_supported(M, N, K) || ldw % 8 || ldx % 8 || ksplit < 1 || (ksplit > 1 && epi == EPI_SWIGLU) ||
         (ksplit > 1 && epi != EPI_PARTIAL && (ws == nullptr || counters == nullptr)) ||
         ((uintptr_t)W & 15) || ((uintptr_t)x & 15))
@@ -280,7 +291,7 @@ PRISM_EXPORT int prism_gemm_tcgen05(const void* W, int ldw, const void* x, int l
     const int ntok = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
     const long long w_rows = epi == EPI_SWIGLU ? 2LL * N : N;
     const int pair = epi == EPI_SWIGLU ? N : 0;
-#define ARGS W, ldw, w_rows, x, ldx, bias, bb, y, ldy, M, N, K, ksplit, pair, ws, counters, err, stream
+#define ARGS W, ldw, w_rows, x, ldx, bias, bb, y, ldy, M, N, K, ksplit, pair, ws, counters, err, group_rows, group_tokens, stream
 #define BY_N(E) (ntok == 16 ? launch<16, E>(ARGS) : ntok == 32 ? launch<32, E>(ARGS) : launch<64, E>(ARGS))
     switch (epi) {
         case EPI_BF16: return BY_N(EPI_BF16);

@@ -8,7 +8,7 @@
 // position p becomes (a cos t - b sin t, b cos t + a sin t), t = p * freq[i]; `freq` is a float32 table
 // of rot / 2 entries (any frequency scaling is in the table), the angle and sincosf are float32.  The slot of
 // position p of request seg is block_table[seg][p / page_size] * page_size + p % page_size.
-// One CTA per token, one warp per head at a time.
+// One warp per (token, head); one more warp per token copies the values.
 #include "common.cuh"
 
 namespace prism {
@@ -37,8 +37,11 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ q_in, const 
     const bool page_ok = page >= 0 && page < num_pages;
     if (!page_ok && threadIdx.x == 0) report_error(err, PRISM_ERR_PAGE_RANGE);
     const size_t slot = page_ok ? (size_t)page * page_size + pos % page_size : 0;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-    for (int hh = warp; hh < nh + nkv; hh += nwarps) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);      // q heads, k heads, then the values
+    if (unit == nh + nkv && page_ok)
+        for (int c = lane; c < nkv * dv; c += 32) v_plane[slot * nkv * dv + c] = from_float<T>(v[c]);
+    for (int hh = unit; hh < nh + nkv; hh += nh + nkv) {
         const bool is_q = hh < nh;
         const float* row = is_q ? q + (size_t)hh * dk : k + (size_t)(hh - nh) * dk;
         const void* w = is_q ? wq : wk;
@@ -64,8 +67,6 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ q_in, const 
             dst[d] = from_float<T>(a);
         }
     }
-    if (page_ok)
-        for (int c = threadIdx.x; c < nkv * dv; c += blockDim.x) v_plane[slot * nkv * dv + c] = from_float<T>(v[c]);
 }
 
 }  // namespace prism
@@ -80,15 +81,17 @@ PRISM_EXPORT int prism_qk_norm_rope_store(const float* q, const float* k, const 
     if (T <= 0) return 0;
     if (rot < 0 || rot > dk || rot % 2 || (rot > 0 && freq == nullptr) || nh < 1 || nkv < 1 || dk < 1 || dv < 1)
         return (int)cudaErrorInvalidValue;
-    const int heads = nh + nkv;
-    const int threads = heads >= 8 ? 256 : (heads >= 4 ? 128 : 64);
+    const int units = nh + nkv + 1;
+    const int threads = units >= 4 ? 128 : 32 * units;
+    const dim3 grid(T, (units + threads / 32 - 1) / (threads / 32));
+    if (T > 65535 * 32) return (int)cudaErrorInvalidValue;
     const int qb = wq_dtype == PRISM_DTYPE_BF16, kb = wk_dtype == PRISM_DTYPE_BF16;
     if (dtype == PRISM_DTYPE_BF16)
-        return (int)prism::launch_kernel(prism::qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, q, k,
+        return (int)prism::launch_kernel(prism::qk_norm_rope_store_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, q, k,
                                          v, ps, wq, qb, wk, kb, eps, freq, rot, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_plane,
                                          (__nv_bfloat16*)v_plane, block_table, bt_width, positions, tok_seg, nh, nkv, dk, dv,
                                          page_size, num_pages, max_pos, err);
-    return (int)prism::launch_kernel(prism::qk_norm_rope_store_kernel<float>, dim3(T), dim3(threads), 0, stream, q, k, v, ps, wq,
+    return (int)prism::launch_kernel(prism::qk_norm_rope_store_kernel<float>, grid, dim3(threads), 0, stream, q, k, v, ps, wq,
                                      qb, wk, kb, eps, freq, rot, (float*)q_out, (float*)k_plane, (float*)v_plane, block_table,
                                      bt_width, positions, tok_seg, nh, nkv, dk, dv, page_size, num_pages, max_pos, err);
 }

@@ -188,6 +188,16 @@ __device__ __forceinline__ void cp_async_f(float* smem, const float* gmem, int f
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(gmem));
 }
 
+// sum over the L (a power of two) neighbouring lanes that share a column; no loop, the tests are uniform
+__device__ __forceinline__ float column_sum(float v, int L) {
+    if (L > 16) v += __shfl_xor_sync(0xffffffffu, v, 16);
+    if (L > 8) v += __shfl_xor_sync(0xffffffffu, v, 8);
+    if (L > 4) v += __shfl_xor_sync(0xffffffffu, v, 4);
+    if (L > 2) v += __shfl_xor_sync(0xffffffffu, v, 2);
+    if (L > 1) v += __shfl_xor_sync(0xffffffffu, v, 1);
+    return v;
+}
+
 template <int MODE, int R>
 __global__ void scan_kernel(const ScanArgs a) {
     pdl_trigger();
@@ -210,7 +220,8 @@ __global__ void scan_kernel(const ScanArgs a) {
     const int kvh = h / a.rep;                         // DELTA: the q/k head this head uses
     // shared, per token of a block:  first[dkp] (q or r) | second[dkp] (k) | third[dkp] (BONUS: w) | v[colsp] | 4 scalars
     const int per_tok = NV * dkp + a.colsp + 4;
-    float* ub = sm + (size_t)2 * TB * per_tok;         // BONUS: u[dkp]
+    constexpr int NBUF = 3;                            // blocks of tokens in shared memory: in use, landed, on its way
+    float* ub = sm + (size_t)NBUF * TB * per_tok;      // BONUS: u[dkp]
     const float* x = pdl_fresh(a.x);
     const float* bg = pdl_fresh(a.bg);
     const float* ww = pdl_fresh(a.ww);
@@ -219,7 +230,7 @@ __global__ void scan_kernel(const ScanArgs a) {
     // CTA's) are never written by the copies: zero them once
     if (dkp > dk || a.colsp > ncols) {
         const int pad = NV * (dkp - dk) + (a.colsp - ncols);
-        for (int i = threadIdx.x; i < 2 * TB * pad; i += blockDim.x) {
+        for (int i = threadIdx.x; i < NBUF * TB * pad; i += blockDim.x) {
             const int slot = i / pad, c = i - slot * pad;
             const int which = c / (dkp - dk > 0 ? dkp - dk : 1);
             const int at = (dkp > dk && which < NV) ? which * dkp + dk + (c - which * (dkp - dk))
@@ -231,7 +242,7 @@ __global__ void scan_kernel(const ScanArgs a) {
         for (int i = threadIdx.x; i < dkp; i += blockDim.x) ub[i] = i < dk ? load_param(a.u, a.u_bf16, (size_t)h * dk + i) : 0.f;
     __syncthreads();
 
-    // the producer warp: block b0 of the segment's tokens into buffer `buf`, complete when it returns
+    // the producer warp asks for block b0 of the segment's tokens into buffer `buf` ...
     auto stage = [&](int b0, int buf) {
         const int lane = threadIdx.x - CT;
         const int nb = min(TB, qlen - b0);
@@ -254,9 +265,14 @@ __global__ void scan_kernel(const ScanArgs a) {
                 cp_async_f(dst + NV * dkp + a.colsp + lane, bg + t * 2 * a.H + (size_t)lane * a.H + h, 1);
         }
         cp_async_commit();
-        cp_async_wait<0>();
+    };
+    // ... and, once the copies of that block have landed (the caller has waited), turns the decay's exponent into the decay
+    auto finish = [&](int b0, int buf) {
+        const int lane = threadIdx.x - CT;
+        const int nb = min(TB, qlen - b0);
+        float* dst0 = sm + (size_t)buf * TB * per_tok;
         __syncwarp();
-        if (MODE == PRISM_SCAN_BONUS) {                // the decay from its exponent, in place
+        if (MODE == PRISM_SCAN_BONUS) {
             for (int idx = lane; idx < nb * dk; idx += 32) {
                 const int tt = idx / dk, i = idx - tt * dk;
                 float* w = dst0 + (size_t)tt * per_tok + 2 * dkp + i;
@@ -269,6 +285,10 @@ __global__ void scan_kernel(const ScanArgs a) {
     float* st = a.state + (((size_t)a.slots[seg] * a.H + h) * dv + col) * dk;
     if (producer) {
         stage(0, 0);
+        if (TB < qlen) stage(TB, 1);
+        else cp_async_commit();
+        cp_async_wait<1>();
+        finish(0, 0);
     } else {
 #pragma unroll
         for (int m = 0; m < Q; ++m) {
@@ -285,10 +305,16 @@ __global__ void scan_kernel(const ScanArgs a) {
     __syncthreads();
 
     int buf = 0;
-    for (int b0 = 0; b0 < qlen; b0 += TB, buf ^= 1) {
+    for (int b0 = 0; b0 < qlen; b0 += TB, buf = buf + 1 == NBUF ? 0 : buf + 1) {
         const int nb = min(TB, qlen - b0);
         if (producer) {
-            if (b0 + TB < qlen) stage(b0 + TB, buf ^ 1);
+            // while block b0 is worked on: ask for the block after the next (its buffer was freed at the last
+            // barrier), and see the next one in
+            const int nxt = buf + 1 == NBUF ? 0 : buf + 1, nxt2 = nxt + 1 == NBUF ? 0 : nxt + 1;
+            if (b0 + 2 * TB < qlen) stage(b0 + 2 * TB, nxt2);
+            else cp_async_commit();
+            cp_async_wait<1>();
+            if (b0 + TB < qlen) finish(b0 + TB, nxt);
             __syncthreads();
             continue;
         }
@@ -311,7 +337,7 @@ __global__ void scan_kernel(const ScanArgs a) {
                     k3 += S[4 * m + 3] * kq[m].w;
                 }
                 float ks = (k0 + k1) + (k2 + k3);
-                for (int off = L >> 1; off > 0; off >>= 1) ks += __shfl_xor_sync(0xffffffffu, ks, off);
+                ks = column_sum(ks, L);
                 const float uu = beta * (vv[lc] - g * ks);
 #pragma unroll
                 for (int m = 0; m < Q; ++m) {
@@ -345,7 +371,7 @@ __global__ void scan_kernel(const ScanArgs a) {
                 }
             }
             float o = (o0 + o1) + (o2 + o3);
-            for (int off = L >> 1; off > 0; off >>= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+            o = column_sum(o, L);
             if (live && part == 0) a.out[((size_t)(s0 + b0 + tt) * a.H + h) * dv + col] = o;
         }
         __syncthreads();                               // the next block has landed, and this buffer is free
@@ -368,7 +394,7 @@ __global__ void scan_kernel(const ScanArgs a) {
 template <int MODE, int R>
 static int launch_scan(const ScanArgs& a, int S, cudaStream_t stream) {
     const int per_tok = (MODE == PRISM_SCAN_BONUS ? 3 : 2) * a.dkp + a.colsp + 4;
-    const size_t smem = ((size_t)2 * a.TB * per_tok + (MODE == PRISM_SCAN_BONUS ? a.dkp : 0)) * sizeof(float);
+    const size_t smem = ((size_t)3 * a.TB * per_tok + (MODE == PRISM_SCAN_BONUS ? a.dkp : 0)) * sizeof(float);
     auto kern = scan_kernel<MODE, R>;
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -127,7 +127,7 @@ class _Sig:
     prism_argmax_split = [_p, _i, _i, _i, _i, _p, _p, _p, _p, _p]
     prism_set_pdl = [_i]
     prism_gemm_tcgen05_supported = [_i, _i, _i]
-    prism_gemm_tcgen05 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _p]
+    prism_gemm_tcgen05 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _i, _p, _p, _p, _i, _i, _p]
     prism_gemv_bf16_supported = [_i, _i, _i]
     prism_gemv_bf16 = [_p, _i, _p, _i, _p, _i, _p, _i, _i, _i, _i, _i, _p]
 
@@ -266,12 +266,18 @@ def _tc_workspace(device, floats: int, tiles: int):
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-            epi: int = EPI_BF16, ksplit: int = 1, err: Optional[torch.Tensor] = None):
+            epi: int = EPI_BF16, ksplit: int = 1, err: Optional[torch.Tensor] = None, group_rows: int = 0):
     """tcgen05 + TMA weight-streaming product for up to 64 tokens.  ``epi``:
     ``EPI_BF16`` / ``EPI_F32`` (``out [M, N]``, + bias), ``EPI_SWIGLU`` (``w`` is
     the fused ``[2N, K]`` gate/up weight), ``EPI_PARTIAL`` (``out`` float32
-    ``[ksplit, M, N]`` partial sums over K for the next kernel to add)."""
+    ``[ksplit, M, N]`` partial sums over K for the next kernel to add).  ``group_rows`` (a multiple of 128):
+    ``x`` is ``[groups, M, K]`` and the weight rows ``[g group_rows, (g + 1) group_rows)`` read ``x[g]``."""
     _cuda(x, w, bias, out)
+    group_tokens = 0
+    if group_rows:
+        assert x.dim() == 3 and x.is_contiguous() and x.shape[0] == -(-w.shape[0] // group_rows) and group_rows % 128 == 0
+        group_tokens = x.shape[1]
+        x = x.view(-1, x.shape[2])[:group_tokens]
     M, K = x.shape
     N = out.shape[-1]
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] == K
@@ -288,7 +294,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out:
         ws, cnt = _tc_workspace(x.device, ksplit * M * N, (N + 127) // 128)
     _check(lib().prism_gemm_tcgen05(_ptr(w), w.stride(0), _ptr(x), x.stride(0) if M > 1 else K, _ptr(bias),
                                     F32 if bias is None else _dt(bias), _ptr(out), N, M, N, K, epi, ksplit,
-                                    _ptr(ws), _ptr(cnt), _ptr(err), _stream()), "gemm_tcgen05")
+                                    _ptr(ws), _ptr(cnt), _ptr(err), int(group_rows), int(group_tokens), _stream()),
+           "gemm_tcgen05")
 
 
 USE_TC_GEMM = os.environ.get("PRISM_TC_GEMM", "1") != "0"
@@ -404,6 +411,25 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     if b is None:
         return torch.mm(x, w.t(), out=out)
     return torch.addmm(b, x, w.t(), out=out)
+
+
+def linear_grouped(xs: torch.Tensor, w: torch.Tensor, group_rows: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Projections of the same tokens that each read an input of their own, as one product: ``xs [G, T, K]``, the
+    rows ``[g group_rows, (g + 1) group_rows)`` of ``w [N, K]`` are applied to ``xs[g]`` (the last group may have
+    fewer rows); returns ``[T, N]``.  One launch of the weight-streaming kernel where it takes the sizes (a
+    decode step), else one product per group."""
+    G, T, K = xs.shape
+    N = w.shape[0]
+    assert G == -(-N // group_rows) and w.shape[1] == K
+    out = torch.empty((T, N), dtype=out_dtype, device=xs.device)
+    if (xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and group_rows % 128 == 0 and xs.is_contiguous()
+            and tc_gemm_ok(xs[0], w) and out_dtype in (torch.float32, torch.bfloat16)):
+        gemm_tc(xs, w, None, out, EPI_F32 if out_dtype == torch.float32 else EPI_BF16, ksplit=tc_ksplit(N, K),
+                group_rows=group_rows)
+        return out
+    for g in range(G):
+        linear(xs[g], w[g * group_rows:(g + 1) * group_rows], None, out=out[:, g * group_rows:(g + 1) * group_rows])
+    return out
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor):

@@ -151,8 +151,8 @@ class WKVMixer(Mixer):
     def params(self):
         W, n, A, R = self.hidden_size, self.names, self.H * self.d, self.rank
         return [ParamSpec("mu", tuple(WeightSource(n["mu_" + s], (W,), "bias") for s in "rkvgw")),
-                ParamSpec("rkvg_w", tuple(WeightSource(n[s], (A, W)) for s in "rkvg")),
-                ParamSpec("w1", (WeightSource(n["w1"], (R, W)),)),
+                # r | k | v | g | the decay's first product: one matrix, each block of rows applied to its own mix
+                ParamSpec("in_w", tuple(WeightSource(n[s], (A, W)) for s in "rkvg") + (WeightSource(n["w1"], (R, W)),)),
                 ParamSpec("w2", (WeightSource(n["w2"], (A, R)),)),
                 ParamSpec("w0", (WeightSource(n["w0"], (A,), "bias"),)),
                 ParamSpec("u", (WeightSource(n["u"], (self.H, self.d), "bias"),)),
@@ -173,18 +173,16 @@ class WKVMixer(Mixer):
         ops.shift_mix(x, prev.state, self.mu, ctx, mixes, keep_prev=ctx.decode_only)
         if not ctx.decode_only:
             ops.state_tail(x, prev.state, ctx)
-        proj = ctx.alloc((4, T, A), torch.float32)             # r, k, v, g: each from its own mix, one matrix each
-        for i in range(4):
-            ops.linear(mixes[i], self.w["rkvg_w"][i * A:(i + 1) * A], None, out=proj[i])
-        low = ops.linear(mixes[4], self.w["w1"], None, out_dtype=torch.float32)
+        # float32 rows [r | k | v | g | low]: each block of columns from its own mix
+        proj = ops.linear_grouped(mixes, self.w["in_w"], A, torch.float32)
+        low = proj[:, 4 * A:]
         ops.activation(low, low, "tanh")
         ww = ops.linear(low, self.w2_f32, None, out_dtype=torch.float32)
         o = ctx.alloc((T, H, d), torch.float32)
-        # the scan addresses rows as base + t * stride + offset: r, k and v are T * A elements apart
-        ops.recurrent_scan(ops.SCAN_BONUS, proj[0], 0, T * A, 2 * T * A, state.state, ctx, H, 1, d, d, o,
+        ops.recurrent_scan(ops.SCAN_BONUS, proj, 0, A, 2 * A, state.state, ctx, H, 1, d, d, o,
                            ww=ww, w0=self.w["w0"], u=self.w["u"])
         inner = ctx.alloc((T, A), ctx.dtype)
-        ops.headnorm_gate(o, proj[3], self.w["norm"], self.eps, self.out_scale, inner)
+        ops.headnorm_gate(o, proj[:, 3 * A:4 * A], self.w["norm"], self.eps, self.out_scale, inner)
         return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
 
 

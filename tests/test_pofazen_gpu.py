@@ -386,6 +386,24 @@ def test_small_kernels(dtype):
         assert float((out.float().cpu() - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("T, A, R, K", [(8, 128, 16, 256), (1, 256, 40, 512), (16, 128, 128, 136), (5, 64, 8, 64), (70, 128, 8, 128)])
+def test_projections_that_each_read_their_own_input_as_one_product(T, A, R, K):
+    """Four blocks of A weight rows and one of R, each applied to its own [T, K] input: the grouped launch of the
+    weight-streaming kernel (A a multiple of 128, up to 16 tokens) and the product-per-group path give the plain
+    products."""
+    from prism_b200 import ops
+    g = torch.Generator().manual_seed(T + A)
+    xs = torch.randn(5, T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(4 * A + R, K, generator=g) / K ** 0.5).to(torch.bfloat16)
+    out = ops.linear_grouped(xs.to(DEV), w.to(DEV), A, torch.float32).cpu()
+    ref = torch.cat([xs[i].float() @ w[i * A:min((i + 1) * A, 4 * A + R)].float().T for i in range(5)], 1)
+    assert out.shape == (T, 4 * A + R)
+    assert float((out - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
+    xs32, w32 = xs.float().to(DEV), w.float().to(DEV)
+    out32 = ops.linear_grouped(xs32, w32, A, torch.float32).cpu()
+    assert float((out32 - ref).abs().max()) <= 1e-4 * max(1.0, float(ref.abs().max()))
+
+
 # ---------------------------------------------------------------------------------------------------------
 # the model through the engine's step function
 # ---------------------------------------------------------------------------------------------------------
