@@ -311,7 +311,11 @@ def pofazen_kernel_numbers(s, pk, once=None):
                 x = torch.randn(Tt, 3 * H * kd, device=DEV) * 0.1
                 ww = torch.randn(Tt, H * kd, device=DEV)
                 w0, u = torch.zeros(H * kd, device=DEV), torch.randn(H * kd, device=DEV) * 0.1
-                fn = lambda: ops.recurrent_scan(mode, x, 0, H * kd, 2 * H * kd, state, c, H, 1, kd, vd, o, ww=ww, w0=w0, u=u)
+                ready = q_len > 1                   # as the mixer does: a step of many tokens forms the decay beforehand
+                if ready:
+                    ops.decay_from_exponent(ww, w0)
+                fn = lambda: ops.recurrent_scan(mode, x, 0, H * kd, 2 * H * kd, state, c, H, 1, kd, vd, o, ww=ww, w0=w0, u=u,
+                                                decay_ready=ready)
             if once:
                 for _ in range(3):
                     fn()

@@ -125,6 +125,16 @@ __global__ void shift_mix_kernel(const float* __restrict__ x_in, int D, const fl
     }
 }
 
+// w[t][c] <- exp(-exp(w[t][c] + w0[c])) in place: the decay of every key channel from its exponent, once for all
+// the CTAs of the scan that read it (a step with many tokens; a decode step lets the scan do it).
+__global__ void decay_from_exponent_kernel(float* __restrict__ w, long long ws, const void* __restrict__ w0, int w0_bf16, int A) {
+    pdl_trigger();
+    pdl_wait();
+    float* row = pdl_fresh(w) + (size_t)blockIdx.y * ws;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < A; c += gridDim.x * blockDim.x)
+        row[c] = expf(-expf(row[c] + load_param(w0, w0_bf16, c)));
+}
+
 // out[t][h dv + c] = o[t][h][c] / sqrt(mean_c(o[t][h]^2) + eps) * weight[widx] * silu(gate[t][h dv + c]) * scale,
 // widx = c (one weight for all heads) or h dv + c (per_head_weight).  One warp per (token, head).
 template <typename T>
@@ -180,6 +190,7 @@ struct ScanArgs {
     float* out;              // [T, H, dv]
     int H, rep, dk, dkp, dv, cols, colsp, L, TB;
     int vec;                 // every source row piece starts on 16 bytes and is whole quads long
+    int w_ready;             // BONUS: ww holds the decay itself already (prism_decay_from_exponent)
 };
 
 __device__ __forceinline__ void cp_async_f(float* smem, const float* gmem, int floats) {      // 1 or 4 floats
@@ -188,8 +199,8 @@ __device__ __forceinline__ void cp_async_f(float* smem, const float* gmem, int f
     else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(gmem));
 }
 
-// sum over the L (a power of two) neighbouring lanes that share a column; no loop, the tests are uniform
-__device__ __forceinline__ float column_sum(float v, int L) {
+// sum over the L (a power of two, known when the kernel is compiled) neighbouring lanes that share a column
+template <int L> __device__ __forceinline__ float column_sum(float v) {
     if (L > 16) v += __shfl_xor_sync(0xffffffffu, v, 16);
     if (L > 8) v += __shfl_xor_sync(0xffffffffu, v, 8);
     if (L > 4) v += __shfl_xor_sync(0xffffffffu, v, 4);
@@ -198,7 +209,7 @@ __device__ __forceinline__ float column_sum(float v, int L) {
     return v;
 }
 
-template <int MODE, int R>
+template <int MODE, int R, int L>
 __global__ void scan_kernel(const ScanArgs a) {
     pdl_trigger();
     pdl_wait();
@@ -207,7 +218,8 @@ __global__ void scan_kernel(const ScanArgs a) {
     constexpr int Q = R / 4;                                   // quads of rows a thread owns
     const int h = blockIdx.x, seg = blockIdx.y, col0 = blockIdx.z * a.cols;
     const int s0 = a.seg_start[seg], qlen = a.seg_start[seg + 1] - s0;
-    const int L = a.L, dk = a.dk, dkp = a.dkp, dv = a.dv, TB = a.TB;
+    const int dk = a.dk, dv = a.dv, TB = a.TB;
+    constexpr int dkp = L * R;                                 // the rows a column's threads cover; beyond dk: zeros
     const int ncols = min(a.cols, dv - col0);
     // The CTA's last warp brings the step's vectors in (and, for the decayed sum, turns the decay's exponent into
     // the decay); the warps before it own the state.  Their threads beyond the CTA's columns run along (they
@@ -272,7 +284,7 @@ __global__ void scan_kernel(const ScanArgs a) {
         const int nb = min(TB, qlen - b0);
         float* dst0 = sm + (size_t)buf * TB * per_tok;
         __syncwarp();
-        if (MODE == PRISM_SCAN_BONUS) {
+        if (MODE == PRISM_SCAN_BONUS && !a.w_ready) {
             for (int idx = lane; idx < nb * dk; idx += 32) {
                 const int tt = idx / dk, i = idx - tt * dk;
                 float* w = dst0 + (size_t)tt * per_tok + 2 * dkp + i;
@@ -337,7 +349,7 @@ __global__ void scan_kernel(const ScanArgs a) {
                     k3 += S[4 * m + 3] * kq[m].w;
                 }
                 float ks = (k0 + k1) + (k2 + k3);
-                ks = column_sum(ks, L);
+                ks = column_sum<L>(ks);
                 const float uu = beta * (vv[lc] - g * ks);
 #pragma unroll
                 for (int m = 0; m < Q; ++m) {
@@ -371,7 +383,7 @@ __global__ void scan_kernel(const ScanArgs a) {
                 }
             }
             float o = (o0 + o1) + (o2 + o3);
-            o = column_sum(o, L);
+            o = column_sum<L>(o);
             if (live && part == 0) a.out[((size_t)(s0 + b0 + tt) * a.H + h) * dv + col] = o;
         }
         __syncthreads();                               // the next block has landed, and this buffer is free
@@ -391,11 +403,11 @@ __global__ void scan_kernel(const ScanArgs a) {
     }
 }
 
-template <int MODE, int R>
+template <int MODE, int R, int L>
 static int launch_scan(const ScanArgs& a, int S, cudaStream_t stream) {
     const int per_tok = (MODE == PRISM_SCAN_BONUS ? 3 : 2) * a.dkp + a.colsp + 4;
     const size_t smem = ((size_t)3 * a.TB * per_tok + (MODE == PRISM_SCAN_BONUS ? a.dkp : 0)) * sizeof(float);
-    auto kern = scan_kernel<MODE, R>;
+    auto kern = scan_kernel<MODE, R, L>;
     if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(a.H, S, (a.dv + a.cols - 1) / a.cols);
@@ -443,6 +455,14 @@ PRISM_EXPORT int prism_shift_mix(const float* x, int D, const float* prev, const
                                      tok_seg, seg_start, slots, (float*)out, out_plane, keep_prev);
 }
 
+PRISM_EXPORT int prism_decay_from_exponent(float* w, long long w_stride, const void* w0, int w0_dtype, int T, int A,
+                                           cudaStream_t stream) {
+    if (T <= 0 || A <= 0) return 0;
+    if (T > 65535) return (int)cudaErrorInvalidValue;
+    return (int)prism::launch_kernel(prism::decay_from_exponent_kernel, dim3((A + 255) / 256, T), dim3(256), 0, stream, w,
+                                     w_stride, w0, w0_dtype == PRISM_DTYPE_BF16, A);
+}
+
 PRISM_EXPORT int prism_headnorm_gate(const float* o, const float* gate, long long gate_stride, const void* weight,
                                      int weight_dtype, int per_head_weight, float eps, float scale, int T, int H, int dv,
                                      void* out, int out_dtype, long long out_stride, cudaStream_t stream) {
@@ -465,7 +485,7 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
                                       const float* bg,
                                       const float* ww, long long ww_stride, const void* w0, int w0_dtype, const void* u,
                                       int u_dtype, float* state, const int* seg_start, const int* slots, int S, int max_q_len,
-                                      int H, int rep, int dk, int dv, float* out, cudaStream_t stream) {
+                                      int H, int rep, int dk, int dv, float* out, int w_ready, cudaStream_t stream) {
     using namespace prism;
     if (S <= 0) return 0;
     if (H < 1 || rep < 1 || dk < 1 || dv < 1 || dk > 1024 || S > 65535) return (int)cudaErrorInvalidValue;
@@ -473,11 +493,13 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     a.x = x; a.xs = x_stride; a.qo = qo; a.ko = ko; a.vo = vo; a.bg = bg; a.ww = ww; a.ws = ww_stride;
     a.w0 = w0; a.w0_bf16 = w0_dtype == PRISM_DTYPE_BF16; a.u = u; a.u_bf16 = u_dtype == PRISM_DTYPE_BF16;
     a.state = state; a.seg_start = seg_start; a.slots = slots; a.out = out; a.H = H; a.rep = rep; a.dk = dk; a.dv = dv;
+    a.w_ready = w_ready;
     // A token's work is one chain (dot product, shuffles, update, dot product, shuffles), so a CTA is latency
     // bound: eight threads a column, four warps of them side by side, and as many CTAs as there are column blocks.
     const int R = dk <= 32 ? 4 : (dk <= 64 ? 8 : (dk <= 128 ? 16 : 32));
     int L = 1;
     while (L * R < dk) L *= 2;                          // at most 32
+    if (R >= 8 && L < 8) L = 8;                        // the compiled pairs: more than 32 rows always take eight threads a column
     a.L = L;
     a.dkp = L * R;                                     // the rows the threads of a column cover; beyond dk: zeros
     // 128 threads a CTA beside the producer warp; fewer (down to one warp) while the grid would leave SMs idle
@@ -495,9 +517,16 @@ PRISM_EXPORT int prism_recurrent_scan(int mode, const float* x, long long x_stri
     int tb = (24 * 1024 / 4) / per_tok;
     tb = tb < 1 ? 1 : (tb > 16 ? 16 : tb);
     a.TB = tb > max_q_len ? (max_q_len < 1 ? 1 : max_q_len) : tb;      // a decode step stages one token, and CTAs are small
+    // rows a thread and threads a column, both known to the compiler: (4, 1..8) up to 32 rows, (8, 8), (16, 8), (32, 8..32)
 #define PRISM_SCAN(M)                                                                                \
-    return R == 4 ? launch_scan<M, 4>(a, S, stream) : R == 8 ? launch_scan<M, 8>(a, S, stream)         \
-         : (R == 16 ? launch_scan<M, 16>(a, S, stream) : launch_scan<M, 32>(a, S, stream))
+    do {                                                                                             \
+        if (R == 4) return L == 1 ? launch_scan<M, 4, 1>(a, S, stream) : L == 2 ? launch_scan<M, 4, 2>(a, S, stream)    \
+                         : L == 4 ? launch_scan<M, 4, 4>(a, S, stream) : launch_scan<M, 4, 8>(a, S, stream);           \
+        if (R == 8) return launch_scan<M, 8, 8>(a, S, stream);                                       \
+        if (R == 16) return launch_scan<M, 16, 8>(a, S, stream);                                     \
+        return L == 8 ? launch_scan<M, 32, 8>(a, S, stream) : L == 16 ? launch_scan<M, 32, 16>(a, S, stream)           \
+                      : launch_scan<M, 32, 32>(a, S, stream);                                        \
+    } while (0)
     if (mode == PRISM_SCAN_DELTA) PRISM_SCAN(PRISM_SCAN_DELTA);
     if (mode == PRISM_SCAN_BONUS) PRISM_SCAN(PRISM_SCAN_BONUS);
 #undef PRISM_SCAN

@@ -103,7 +103,8 @@ class _Sig:
     prism_state_tail = [_p, _ll, _i, _p, _i, _p, _p, _i, _p]
     prism_shift_mix = [_p, _i, _p, _p, _i, _i, _p, _p, _p, _i, _p, _i, _ll, _i, _p]
     prism_headnorm_gate = [_p, _p, _ll, _p, _i, _i, _f, _f, _i, _i, _i, _p, _i, _ll, _p]
-    prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _p]
+    prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p]
+    prism_decay_from_exponent = [_p, _ll, _p, _i, _i, _i, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _i,
                              _p, _ll, _p]
@@ -1597,12 +1598,14 @@ SCAN_DELTA, SCAN_BONUS = 0, 1      # csrc/recurrent.cu: PRISM_SCAN_*
 
 def recurrent_scan(mode: int, x: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, ctx, H: int,
                    rep: int, dk: int, dv: int, out: torch.Tensor, bg: Optional[torch.Tensor] = None,
-                   ww: Optional[torch.Tensor] = None, w0: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None):
+                   ww: Optional[torch.Tensor] = None, w0: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None,
+                   decay_ready: bool = False):
     """The step's tokens through a matrix-state recurrence, request by request, token after token, from and
     into ``state [slots, H, dv, dk]`` (float32).  ``x``: float32 rows holding q (or r) at column ``q_off``, k at
     ``k_off``, v at ``v_off``.  ``SCAN_DELTA``: delta rule with ``bg [T, 2 H]`` (beta | scalar decay), ``rep`` heads
     share a q/k head.  ``SCAN_BONUS``: per-channel decay ``exp(-exp(ww + w0))`` (``ww [T, H * dk]``) and bonus ``u [H
-    * dk]`` for the current token.  ``out [T, H, dv]`` float32."""
+    * dk]`` for the current token; ``decay_ready``: ``ww`` holds the decay itself (``decay_from_exponent``).  ``out
+    [T, H, dv]`` float32."""
     _cuda(x, state, out, bg, ww, w0, u)
     T = x.shape[0]
     assert x.dtype == torch.float32 and x.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
@@ -1616,5 +1619,14 @@ def recurrent_scan(mode: int, x: torch.Tensor, q_off: int, k_off: int, v_off: in
         int(mode), _ptr(x), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(bg), _ptr(ww),
         0 if ww is None else ww.stride(0), _ptr(w0), F32 if w0 is None else _dt(w0), _ptr(u), F32 if u is None else _dt(u),
         _ptr(state), _ptr(ctx.seg_start), _ptr(ctx.state_slots), ctx.S, int(getattr(ctx, "max_q_len", None) or T), H, rep, dk, dv,
-        _ptr(out), _stream()),
+        _ptr(out), 1 if decay_ready else 0, _stream()),
         "recurrent_scan")
+
+
+def decay_from_exponent(ww: torch.Tensor, w0: torch.Tensor):
+    """``ww <- exp(-exp(ww + w0))`` in place (``ww [T, A]`` float32, row stride free): the per-channel decay of the
+    decayed-sum scan, formed once where a step has many tokens."""
+    _cuda(ww, w0)
+    T, A = ww.shape
+    assert ww.dtype == torch.float32 and ww.stride(1) == 1 and w0.numel() == A and w0.is_contiguous()
+    _check(lib().prism_decay_from_exponent(_ptr(ww), ww.stride(0), _ptr(w0), _dt(w0), T, A, _stream()), "decay_from_exponent")

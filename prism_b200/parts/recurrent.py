@@ -179,8 +179,12 @@ class WKVMixer(Mixer):
         ops.activation(low, low, "tanh")
         ww = ops.linear(low, self.w2_f32, None, out_dtype=torch.float32)
         o = ctx.alloc((T, H, d), torch.float32)
+        # with many tokens the decay is formed once for all the scan's CTAs; a decode step leaves it to the scan
+        ready = not ctx.decode_only
+        if ready:
+            ops.decay_from_exponent(ww, self.w["w0"])
         ops.recurrent_scan(ops.SCAN_BONUS, proj, 0, A, 2 * A, state.state, ctx, H, 1, d, d, o,
-                           ww=ww, w0=self.w["w0"], u=self.w["u"])
+                           ww=ww, w0=self.w["w0"], u=self.w["u"], decay_ready=ready)
         inner = ctx.alloc((T, A), ctx.dtype)
         ops.headnorm_gate(o, proj[:, 3 * A:4 * A], self.w["norm"], self.eps, self.out_scale, inner)
         return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
