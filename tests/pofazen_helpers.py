@@ -65,10 +65,10 @@ CONFIG_P = model(211, 72, eps=1e-5, alpha=2.5, layers=[
 ])
 # Q: sizes the tensor-core kernels take (multiples of 16), pages of 64, a window larger than a page, more kept
 # tokens than a tile's worth of a few, one kv head; heads and sizes of the two sides differ everywhere
-CONFIG_Q = model(300, 128, alpha=3.0, layers=[
+CONFIG_Q = model(300, 128, alpha=2.2, layers=[
     layer("wkv", wkv(4, 32, 16), 160),
-    layer("parallel", parallel(left(4, 1, 32, 64, 70, 5, scale=0.25, rot_dims=16, base=20000.0, scaling=(8.0, 1.0, 4.0, 128)),
-                               right(2, 1, 64, 32, 4), 1.2, 1.1), 192),
+    layer("parallel", parallel(left(4, 1, 32, 64, 70, 5, scale=0.25, rot_dims=16, base=30000.0, scaling=(8.0, 1.0, 4.0, 128)),
+                               right(2, 1, 64, 32, 4), 1.4, 0.9), 192),
     layer("parallel", parallel(left(2, 2, 64, 16, 100, 40, rot_dims=64), right(4, 4, 16, 16, 4), 1.0, 1.0), 96),
     layer("wkv", wkv(8, 16, 4), 128),
 ])

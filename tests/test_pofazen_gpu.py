@@ -471,7 +471,7 @@ def test_a_state_slot_that_is_used_again_starts_from_zero():
 
 ONE_LAYER = {
     "parallel": [layer("parallel", parallel(left(4, 2, 16, 8, 9, 2, rot_dims=8, base=300.0, scaling=(2.0, 1.0, 2.0, 32)),
-                                            right(2, 1, 16, 24, 4), 1.2, 1.1), None)],
+                                            right(2, 1, 16, 24, 4), 1.25, 0.85), None)],
     "attention_side_mostly": [layer("parallel", parallel(left(3, 1, 32, 32, 21, 5, scale=0.11), right(1, 1, 8, 8, 2), 1.5, 0.01), None)],
     "delta_side_mostly": [layer("parallel", parallel(left(1, 1, 8, 8, 4), right(4, 2, 24, 12, 5), 0.01, 1.5), None)],
     "wkv": [layer("wkv", wkv(3, 16, 6), None)],
