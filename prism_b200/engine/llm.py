@@ -18,10 +18,9 @@ import torch
 
 from ..config.engine_config import EngineConfig, ModelConfig
 from ..cache.manager import pool_sizes
-from ..config.model_config import read_config_json
 from ..model_registry import build_model
 from ..sampling.sampler import Sampler, SamplingParams
-from ..weights.loader import load_weights
+from ..weights.loader import load_model_folder
 from ..weights.random_init import random_pool
 from .request import GenerationResult
 from .runner import ModelRunner, cache_groups
@@ -48,9 +47,8 @@ class Engine:
         self.device = torch.device(f"cuda:{ec.gpu_id}")
         torch.cuda.set_device(self.device)
         if model is not None:
-            raw = read_config_json(model.model_id)
-            self.config, self.model = build_model(raw)
-            self.pool = load_weights(self.model, model.model_id, self.device, self.dtype)
+            # the folder's loader: a design may take a size from the model file's tensor shapes
+            self.config, self.model, self.pool = load_model_folder(model.model_id, self.device, self.dtype)
         else:
             if config is None:
                 raise ValueError("give a model folder, or config= and random_seed= for random weights")

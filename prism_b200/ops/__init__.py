@@ -414,22 +414,27 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     return torch.addmm(b, x, w.t(), out=out)
 
 
-def linear_grouped(xs: torch.Tensor, w: torch.Tensor, group_rows: int, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """Projections of the same tokens that each read an input of their own, as one product: ``xs [G, T, K]``, the
-    rows ``[g group_rows, (g + 1) group_rows)`` of ``w [N, K]`` are applied to ``xs[g]`` (the last group may have
-    fewer rows); returns ``[T, N]``.  One launch of the weight-streaming kernel where it takes the sizes (a
-    decode step), else one product per group."""
+def linear_grouped(xs: torch.Tensor, w: torch.Tensor, rows, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Projections of the same tokens that each read an input of their own, as one product: ``xs [G, T, K]``; the
+    first ``rows[0]`` rows of ``w [N, K]`` are applied to ``xs[0]``, the next ``rows[1]`` to ``xs[1]`` and so on;
+    returns ``[T, N]``.  One launch of the weight-streaming kernel where it takes the sizes (a decode step, groups
+    of one size that is a multiple of 128, the last one no larger), else one product per group."""
     G, T, K = xs.shape
     N = w.shape[0]
-    assert G == -(-N // group_rows) and w.shape[1] == K
+    rows = [int(r) for r in rows]
+    assert G == len(rows) and sum(rows) == N and w.shape[1] == K and min(rows) > 0
     out = torch.empty((T, N), dtype=out_dtype, device=xs.device)
-    if (xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and group_rows % 128 == 0 and xs.is_contiguous()
-            and tc_gemm_ok(xs[0], w) and out_dtype in (torch.float32, torch.bfloat16)):
+    size = rows[0]
+    if (xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and size % 128 == 0 and all(r == size for r in rows[:-1])
+            and rows[-1] <= size and xs.is_contiguous() and tc_gemm_ok(xs[0], w)
+            and out_dtype in (torch.float32, torch.bfloat16)):
         gemm_tc(xs, w, None, out, EPI_F32 if out_dtype == torch.float32 else EPI_BF16, ksplit=tc_ksplit(N, K),
-                group_rows=group_rows)
+                group_rows=size)
         return out
-    for g in range(G):
-        linear(xs[g], w[g * group_rows:(g + 1) * group_rows], None, out=out[:, g * group_rows:(g + 1) * group_rows])
+    at = 0
+    for g, r in enumerate(rows):
+        linear(xs[g], w[at:at + r], None, out=out[:, at:at + r])
+        at += r
     return out
 
 

@@ -174,7 +174,7 @@ class WKVMixer(Mixer):
         if not ctx.decode_only:
             ops.state_tail(x, prev.state, ctx)
         # float32 rows [r | k | v | g | low]: each block of columns from its own mix
-        proj = ops.linear_grouped(mixes, self.w["in_w"], A, torch.float32)
+        proj = ops.linear_grouped(mixes, self.w["in_w"], (A, A, A, A, self.rank), torch.float32)
         low = proj[:, 4 * A:]
         ops.activation(low, low, "tanh")
         ww = ops.linear(low, self.w2_f32, None, out_dtype=torch.float32)

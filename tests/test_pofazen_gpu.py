@@ -386,7 +386,8 @@ def test_small_kernels(dtype):
         assert float((out.float().cpu() - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max()))
 
 
-@pytest.mark.parametrize("T, A, R, K", [(8, 128, 16, 256), (1, 256, 40, 512), (16, 128, 128, 136), (5, 64, 8, 64), (70, 128, 8, 128)])
+@pytest.mark.parametrize("T, A, R, K", [(8, 128, 16, 256), (1, 256, 40, 512), (16, 128, 128, 136), (5, 64, 8, 64), (70, 128, 8, 128),
+                                        (4, 8, 64, 32), (3, 128, 200, 64)])
 def test_projections_that_each_read_their_own_input_as_one_product(T, A, R, K):
     """Four blocks of A weight rows and one of R, each applied to its own [T, K] input: the grouped launch of the
     weight-streaming kernel (A a multiple of 128, up to 16 tokens) and the product-per-group path give the plain
@@ -395,12 +396,12 @@ def test_projections_that_each_read_their_own_input_as_one_product(T, A, R, K):
     g = torch.Generator().manual_seed(T + A)
     xs = torch.randn(5, T, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(4 * A + R, K, generator=g) / K ** 0.5).to(torch.bfloat16)
-    out = ops.linear_grouped(xs.to(DEV), w.to(DEV), A, torch.float32).cpu()
-    ref = torch.cat([xs[i].float() @ w[i * A:min((i + 1) * A, 4 * A + R)].float().T for i in range(5)], 1)
+    out = ops.linear_grouped(xs.to(DEV), w.to(DEV), (A, A, A, A, R), torch.float32).cpu()
+    ref = torch.cat([xs[i].float() @ w[i * A:(i * A + R if i == 4 else (i + 1) * A)].float().T for i in range(5)], 1)
     assert out.shape == (T, 4 * A + R)
     assert float((out - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
     xs32, w32 = xs.float().to(DEV), w.float().to(DEV)
-    out32 = ops.linear_grouped(xs32, w32, A, torch.float32).cpu()
+    out32 = ops.linear_grouped(xs32, w32, (A, A, A, A, R), torch.float32).cpu()
     assert float((out32 - ref).abs().max()) <= 1e-4 * max(1.0, float(ref.abs().max()))
 
 
@@ -537,8 +538,11 @@ def test_greedy_generation_through_the_scheduler():
     w = {k: v.float() for k, v in draw_weights(raw, CONFIGS["P"][1]).items()}
     prompts = [random_tokens(raw["vocab"], n, 40 + n) for n in (3, 17, 30, 8, 1, 12)]
     n_new = 24
+    # a folder as an exporter writes it: the decay's rank is in no key of config.json, the model file has it
+    bare = dict(raw, layers=[dict(l, mixer={k: v for k, v in l["mixer"].items() if k != "decay_rank"}) for l in raw["layers"]])
+    folder = write_folder(bare, draw_weights(raw, CONFIGS["P"][1]))
     for graphs in (False, True):
-        eng = Engine(model_folder("P"), EngineConfig(kv_page_size=8, num_pages=40, max_seq_len=128, use_cuda_graph=graphs,
+        eng = Engine(folder, EngineConfig(kv_page_size=8, num_pages=40, max_seq_len=128, use_cuda_graph=graphs,
                                                       graph_batch_sizes=(1, 2, 4, 8),
                                                       scheduler=SchedulerConfig(max_batch_tokens=48, max_num_seqs=4, prefill_chunk=16)),
                      dtype="float32")
