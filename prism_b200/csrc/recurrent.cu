@@ -135,6 +135,46 @@ __global__ void decay_from_exponent_kernel(float* __restrict__ w, long long ws, 
         row[c] = expf(-expf(row[c] + load_param(w0, w0_bf16, c)));
 }
 
+// decay[t][n] = exp(-exp(sum_r tanh(low[t][r]) w2t[r][n] + w0[n])): the per-channel decay from the low-rank product's
+// first half, in one launch (tanh, the second product, the offset and both exponentials), all float32.  A CTA takes
+// 128 channels and sixteen tokens, so that every weight it reads serves sixteen tokens (whose tanh values sit side
+// by side in shared memory: four 128-bit loads per weight); w2t is the second matrix transposed, [R, N], so that
+// neighbouring threads read neighbouring floats.
+constexpr int LRD_TOK = 16;
+__global__ void lowrank_decay_kernel(const float* __restrict__ low_in, long long ls, int R, const float* __restrict__ w2t,
+                                     const void* __restrict__ w0, int w0_bf16, int N, int T, float* __restrict__ out,
+                                     long long os) {
+    pdl_trigger();
+    pdl_wait();
+    const float* low = pdl_fresh(low_in);
+    extern __shared__ __align__(16) float s[];         // [R][LRD_TOK]
+    const int t0 = blockIdx.y * LRD_TOK, n = blockIdx.x * blockDim.x + threadIdx.x;
+    for (int i = threadIdx.x; i < LRD_TOK * R; i += blockDim.x) {
+        const int j = i / R, r = i - j * R;            // neighbouring threads read neighbouring entries of a token's row
+        s[r * LRD_TOK + j] = t0 + j < T ? tanhf(low[(size_t)(t0 + j) * ls + r]) : 0.f;
+    }
+    __syncthreads();
+    if (n >= N) return;
+    float acc[LRD_TOK];
+#pragma unroll
+    for (int j = 0; j < LRD_TOK; ++j) acc[j] = 0.f;
+    for (int r = 0; r < R; ++r) {
+        const float w = w2t[(size_t)r * N + n];
+#pragma unroll
+        for (int j = 0; j < LRD_TOK; j += 4) {
+            const float4 t4 = *reinterpret_cast<const float4*>(s + r * LRD_TOK + j);
+            acc[j] += w * t4.x;
+            acc[j + 1] += w * t4.y;
+            acc[j + 2] += w * t4.z;
+            acc[j + 3] += w * t4.w;
+        }
+    }
+    const float b = load_param(w0, w0_bf16, n);
+#pragma unroll
+    for (int j = 0; j < LRD_TOK; ++j)
+        if (t0 + j < T) out[(size_t)(t0 + j) * os + n] = expf(-expf(acc[j] + b));
+}
+
 // out[t][h dv + c] = o[t][h][c] / sqrt(mean_c(o[t][h]^2) + eps) * weight[widx] * silu(gate[t][h dv + c]) * scale,
 // widx = c (one weight for all heads) or h dv + c (per_head_weight).  One warp per (token, head).
 template <typename T>
@@ -461,6 +501,18 @@ PRISM_EXPORT int prism_decay_from_exponent(float* w, long long w_stride, const v
     if (T > 65535) return (int)cudaErrorInvalidValue;
     return (int)prism::launch_kernel(prism::decay_from_exponent_kernel, dim3((A + 255) / 256, T), dim3(256), 0, stream, w,
                                      w_stride, w0, w0_dtype == PRISM_DTYPE_BF16, A);
+}
+
+// low [T, R] float32 (row stride free), w2t [R, N] float32, w0 [N]; out [T, N] float32.
+PRISM_EXPORT int prism_lowrank_decay(const float* low, long long low_stride, int R, const float* w2t, const void* w0,
+                                     int w0_dtype, int N, int T, float* out, long long out_stride, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    const size_t smem = (size_t)prism::LRD_TOK * R * sizeof(float);
+    if (R < 1 || smem > 200 * 1024 || (T + prism::LRD_TOK - 1) / prism::LRD_TOK > 65535) return (int)cudaErrorInvalidValue;
+    auto kern = prism::lowrank_decay_kernel;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return (int)prism::launch_kernel(kern, dim3((N + 127) / 128, (T + prism::LRD_TOK - 1) / prism::LRD_TOK), dim3(128), smem,
+                                     stream, low, low_stride, R, w2t, w0, w0_dtype == PRISM_DTYPE_BF16, N, T, out, out_stride);
 }
 
 PRISM_EXPORT int prism_headnorm_gate(const float* o, const float* gate, long long gate_stride, const void* weight,

@@ -105,6 +105,7 @@ class _Sig:
     prism_headnorm_gate = [_p, _p, _ll, _p, _i, _i, _f, _f, _i, _i, _i, _p, _i, _ll, _p]
     prism_recurrent_scan = [_i, _p, _ll, _ll, _ll, _ll, _p, _p, _ll, _p, _i, _p, _i, _p, _p, _p, _i, _i, _i, _i, _i, _i, _p, _i, _p]
     prism_decay_from_exponent = [_p, _ll, _p, _i, _i, _i, _p]
+    prism_lowrank_decay = [_p, _ll, _i, _p, _p, _i, _i, _i, _p, _ll, _p]
     prism_cache_store = [_p, _ll, _p, _i, _i, _p, _ll, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p]
     prism_latent_kv_store = [_p, _ll, _p, _i, _f, _i, _i, _i, _p, _p, _i, _p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _p, _i,
                              _p, _ll, _p]
@@ -1626,6 +1627,20 @@ def recurrent_scan(mode: int, x: torch.Tensor, q_off: int, k_off: int, v_off: in
         _ptr(state), _ptr(ctx.seg_start), _ptr(ctx.state_slots), ctx.S, int(getattr(ctx, "max_q_len", None) or T), H, rep, dk, dv,
         _ptr(out), 1 if decay_ready else 0, _stream()),
         "recurrent_scan")
+
+
+def lowrank_decay(low: torch.Tensor, w2t: torch.Tensor, w0: torch.Tensor, out: torch.Tensor):
+    """``out = exp(-exp(tanh(low) @ w2t + w0))``: the decayed-sum scan's per-channel decay from the first half of its
+    low-rank product, in one launch and in float32 throughout.  ``low [T, R]`` float32 (row stride free), ``w2t [R,
+    N]`` float32 (the second matrix, transposed), ``w0 [N]``, ``out [T, N]`` float32."""
+    _cuda(low, w2t, w0, out)
+    T, R = low.shape
+    N = w2t.shape[1]
+    assert low.dtype == torch.float32 and low.stride(1) == 1 and w2t.dtype == torch.float32 and w2t.is_contiguous()
+    assert w2t.shape[0] == R and w0.numel() == N and w0.is_contiguous() and out.shape == (T, N) and out.dtype == torch.float32
+    assert out.stride(1) == 1
+    _check(lib().prism_lowrank_decay(_ptr(low), low.stride(0), R, _ptr(w2t), _ptr(w0), _dt(w0), N, T, _ptr(out), out.stride(0),
+                                     _stream()), "lowrank_decay")
 
 
 def decay_from_exponent(ww: torch.Tensor, w0: torch.Tensor):

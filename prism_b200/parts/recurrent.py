@@ -16,6 +16,7 @@ mixers can hand theirs over).
 
 from __future__ import annotations
 
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -160,8 +161,9 @@ class WKVMixer(Mixer):
                 ParamSpec("o_w", (WeightSource(n["o"], (W, A)),))]
 
     def on_bound(self):
-        # the decay's second product runs in float32 whatever the engine's dtype (its input is the float32 tanh)
-        self.w2_f32 = self.w["w2"].float() if self.w["w2"] is not None else None
+        # the decay's second product runs in float32 whatever the engine's dtype (its input is the float32 tanh);
+        # transposed, so that the kernel's neighbouring threads read neighbouring floats
+        self.w2t = self.w["w2"].float().t().contiguous() if self.w["w2"] is not None else None
         self.mu = self.w["mu"].view(5, self.hidden_size)
 
     def forward(self, ctx, x, cache):
@@ -175,16 +177,12 @@ class WKVMixer(Mixer):
             ops.state_tail(x, prev.state, ctx)
         # float32 rows [r | k | v | g | low]: each block of columns from its own mix
         proj = ops.linear_grouped(mixes, self.w["in_w"], (A, A, A, A, self.rank), torch.float32)
-        low = proj[:, 4 * A:]
-        ops.activation(low, low, "tanh")
-        ww = ops.linear(low, self.w2_f32, None, out_dtype=torch.float32)
+        # tanh, the second product, the offset and both exponentials in one launch: the decay of every key channel
+        ww = ctx.alloc((T, A), torch.float32)
+        ops.lowrank_decay(proj[:, 4 * A:], self.w2t, self.w["w0"], ww)
         o = ctx.alloc((T, H, d), torch.float32)
-        # with many tokens the decay is formed once for all the scan's CTAs; a decode step leaves it to the scan
-        ready = not ctx.decode_only
-        if ready:
-            ops.decay_from_exponent(ww, self.w["w0"])
         ops.recurrent_scan(ops.SCAN_BONUS, proj, 0, A, 2 * A, state.state, ctx, H, 1, d, d, o,
-                           ww=ww, w0=self.w["w0"], u=self.w["u"], decay_ready=ready)
+                           ww=ww, w0=self.w["w0"], u=self.w["u"], decay_ready=True)
         inner = ctx.alloc((T, A), ctx.dtype)
         ops.headnorm_gate(o, proj[:, 3 * A:4 * A], self.w["norm"], self.eps, self.out_scale, inner)
         return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
@@ -197,9 +195,16 @@ class SumOfMixers(Mixer):
     one product over the joined inner outputs, ``[a_1 | a_2 | ..] @ [W_o1 | W_o2 | ..]^T`` with each scale folded
     into its ``a_i``, so the results are added in the product's float32 accumulator; where every mixer also hands
     over its input projection, those are one product too (float32 results if any of them wants that).  ``fuse``
-    False: every mixer runs on its own and the float32 results are added."""
+    False: every mixer runs on its own and the float32 results are added.
+
+    Between the two joint products the mixers do not depend on one another, and each is a chain of small kernels,
+    so the second and later ones run on streams of their own beside the first (forked after the input product,
+    joined before the output product; inside a captured graph they become parallel branches).
+    ``PRISM_MIXER_STREAMS=0`` keeps them on one stream."""
 
     graph_safe = True
+    SIDE_STREAMS = os.environ.get("PRISM_MIXER_STREAMS", "1") != "0"
+    _streams = {}            # (device, i) -> stream of the i-th mixer beside the first
 
     def __init__(self, mixers: Sequence[PartSpec], scales: Sequence[float], fuse: bool = True):
         if len(mixers) != len(scales) or not mixers:
@@ -258,8 +263,29 @@ class SumOfMixers(Mixer):
             for i, d in enumerate(self.ins):
                 projs[i] = proj[:, o:o + d.width]
                 o += d.width
-        o = 0
-        for m, d, c, p in zip(self.mixers, self.outs, caches, projs):
-            m.forward_inner(ctx, x, c, inner[:, o:o + d.width], p)
+        offs, o = [], 0
+        for d in self.outs:
+            offs.append(o)
             o += d.width
+        work = list(zip(self.mixers, self.outs, caches, projs, offs))
+        if self.SIDE_STREAMS and len(work) > 1:
+            main = torch.cuda.current_stream(x.device)
+            fork = torch.cuda.Event()
+            fork.record(main)
+            sides = []
+            for i, (m, d, c, p, at) in enumerate(work[1:]):
+                side = self._streams.get((x.device, i))
+                if side is None:
+                    side = self._streams[(x.device, i)] = torch.cuda.Stream(device=x.device)
+                side.wait_event(fork)
+                with torch.cuda.stream(side):
+                    m.forward_inner(ctx, x, c, inner[:, at:at + d.width], p)
+                sides.append(side)
+            m, d, c, p, at = work[0]
+            m.forward_inner(ctx, x, c, inner[:, at:at + d.width], p)
+            for side in sides:
+                main.wait_stream(side)
+        else:
+            for m, d, c, p, at in work:
+                m.forward_inner(ctx, x, c, inner[:, at:at + d.width], p)
         return ops.linear_delta(inner, self.w["out_w"], None, f32=True)

@@ -336,6 +336,20 @@ def test_convolution_with_its_tail_unit_vectors_and_gates(G, H, dk, dv, K):
     assert float((got2 - ref).abs().max()) <= 1e-5
 
 
+@pytest.mark.parametrize("T, R, N", [(1, 16, 64), (9, 5, 60), (70, 64, 300), (8, 1, 1), (3, 100, 130)])
+def test_decay_from_the_low_rank_product(T, R, N):
+    from prism_b200 import ops
+    g = torch.Generator().manual_seed(T * R)
+    low, w2, w0 = torch.randn(T, R + 3, generator=g), torch.randn(N, R, generator=g) / R ** 0.5, torch.randn(N, generator=g) - 1.0
+    out = torch.empty(T, N, device=DEV)
+    ops.lowrank_decay(low.to(DEV)[:, 3:], w2.t().contiguous().to(DEV), w0.to(DEV), out)
+    ref = torch.exp(-torch.exp(torch.tanh(low[:, 3:]) @ w2.T + w0))
+    assert float((out.cpu() - ref).abs().max()) <= 2e-6
+    ww = (torch.tanh(low[:, 3:]) @ w2.T).to(DEV)
+    ops.decay_from_exponent(ww, w0.to(DEV))
+    assert float((ww.cpu() - ref).abs().max()) <= 2e-6
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_small_kernels(dtype):
     from prism_b200 import ops
