@@ -306,7 +306,8 @@ def pofazen_kernel_numbers(s, pk, once=None):
             if mode == ops.SCAN_DELTA:
                 x = torch.nn.functional.normalize(torch.randn(Tt, 2 * G + H, kd, device=DEV), dim=-1).view(Tt, -1)
                 bg = torch.rand(Tt, 2 * H, device=DEV) * 0.5 + 0.5
-                fn = lambda: ops.recurrent_scan(mode, x, 0, G * kd, 2 * G * kd, state, c, H, rep, kd, vd, o, bg=bg)
+                fn = lambda: ops.recurrent_scan(mode, x[:, :G * kd], x[:, G * kd:2 * G * kd], x[:, 2 * G * kd:], state, c, H, rep, kd,
+                                                vd, o, bg=bg)
             else:
                 x = torch.randn(Tt, 3 * H * kd, device=DEV) * 0.1
                 ww = torch.randn(Tt, H * kd, device=DEV)
@@ -314,8 +315,8 @@ def pofazen_kernel_numbers(s, pk, once=None):
                 ready = q_len > 1                   # as the mixer does: a step of many tokens forms the decay beforehand
                 if ready:
                     ops.decay_from_exponent(ww, w0)
-                fn = lambda: ops.recurrent_scan(mode, x, 0, H * kd, 2 * H * kd, state, c, H, 1, kd, vd, o, ww=ww, w0=w0, u=u,
-                                                decay_ready=ready)
+                fn = lambda: ops.recurrent_scan(mode, x[:, :H * kd], x[:, H * kd:2 * H * kd], x[:, 2 * H * kd:], state, c, H, 1, kd,
+                                                vd, o, ww=ww, w0=w0, u=u, decay_ready=ready)
             if once:
                 for _ in range(3):
                     fn()

@@ -415,28 +415,26 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     return torch.addmm(b, x, w.t(), out=out)
 
 
-def linear_grouped(xs: torch.Tensor, w: torch.Tensor, rows, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    """Projections of the same tokens that each read an input of their own, as one product: ``xs [G, T, K]``; the
-    first ``rows[0]`` rows of ``w [N, K]`` are applied to ``xs[0]``, the next ``rows[1]`` to ``xs[1]`` and so on;
-    returns ``[T, N]``.  One launch of the weight-streaming kernel where it takes the sizes (a decode step, groups
-    of one size that is a multiple of 128, the last one no larger), else one product per group."""
+def linear_grouped(xs: torch.Tensor, w: torch.Tensor, rows, out_dtype: torch.dtype = torch.float32):
+    """Projections of the same tokens that each read an input of their own: ``xs [G, T, K]``; the first ``rows[0]``
+    rows of ``w [N, K]`` are applied to ``xs[0]``, the next ``rows[1]`` to ``xs[1]`` and so on.  Returns one ``[T,
+    rows[g]]`` result per group, all with the same row stride where the groups are of one size.  One launch of the
+    weight-streaming kernel where it takes the sizes (a decode step, groups of one size that is a multiple of 128,
+    the last one no larger: the results are column blocks of one buffer), else one product per group."""
     G, T, K = xs.shape
     N = w.shape[0]
     rows = [int(r) for r in rows]
     assert G == len(rows) and sum(rows) == N and w.shape[1] == K and min(rows) > 0
-    out = torch.empty((T, N), dtype=out_dtype, device=xs.device)
     size = rows[0]
+    bounds = [sum(rows[:g]) for g in range(G + 1)]
     if (xs.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and size % 128 == 0 and all(r == size for r in rows[:-1])
             and rows[-1] <= size and xs.is_contiguous() and tc_gemm_ok(xs[0], w)
             and out_dtype in (torch.float32, torch.bfloat16)):
+        out = torch.empty((T, N), dtype=out_dtype, device=xs.device)
         gemm_tc(xs, w, None, out, EPI_F32 if out_dtype == torch.float32 else EPI_BF16, ksplit=tc_ksplit(N, K),
                 group_rows=size)
-        return out
-    at = 0
-    for g, r in enumerate(rows):
-        linear(xs[g], w[at:at + r], None, out=out[:, at:at + r])
-        at += r
-    return out
+        return [out[:, bounds[g]:bounds[g + 1]] for g in range(G)]
+    return [linear(xs[g], w[bounds[g]:bounds[g + 1]], None, out_dtype=out_dtype) for g in range(G)]
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor):
@@ -1602,27 +1600,34 @@ def headnorm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps
 SCAN_DELTA, SCAN_BONUS = 0, 1      # csrc/recurrent.cu: PRISM_SCAN_*
 
 
-def recurrent_scan(mode: int, x: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, ctx, H: int,
+def recurrent_scan(mode: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, ctx, H: int,
                    rep: int, dk: int, dv: int, out: torch.Tensor, bg: Optional[torch.Tensor] = None,
                    ww: Optional[torch.Tensor] = None, w0: Optional[torch.Tensor] = None, u: Optional[torch.Tensor] = None,
                    decay_ready: bool = False):
     """The step's tokens through a matrix-state recurrence, request by request, token after token, from and
-    into ``state [slots, H, dv, dk]`` (float32).  ``x``: float32 rows holding q (or r) at column ``q_off``, k at
-    ``k_off``, v at ``v_off``.  ``SCAN_DELTA``: delta rule with ``bg [T, 2 H]`` (beta | scalar decay), ``rep`` heads
-    share a q/k head.  ``SCAN_BONUS``: per-channel decay ``exp(-exp(ww + w0))`` (``ww [T, H * dk]``) and bonus ``u [H
-    * dk]`` for the current token; ``decay_ready``: ``ww`` holds the decay itself (``decay_from_exponent``).  ``out
-    [T, H, dv]`` float32."""
-    _cuda(x, state, out, bg, ww, w0, u)
-    T = x.shape[0]
-    assert x.dtype == torch.float32 and x.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous()
-    assert tuple(state.shape[1:]) == (H, dv, dk) and out.shape == (T, H, dv) and out.is_contiguous() and out.dtype == torch.float32
+    into ``state [slots, H, dv, dk]`` (float32).  ``q`` (or r), ``k``, ``v``: float32 rows ``[T, heads * size]`` with
+    one row stride - column blocks of one product, or products of their own.  ``SCAN_DELTA``: delta rule with ``bg
+    [T, 2 H]`` (beta | scalar decay), ``rep`` heads share a q/k head.  ``SCAN_BONUS``: per-channel decay ``exp(-exp(ww
+    + w0))`` (``ww [T, H * dk]``) and bonus ``u [H * dk]`` for the current token; ``decay_ready``: ``ww`` holds the decay
+    itself (``lowrank_decay``, ``decay_from_exponent``).  ``out [T, H, dv]`` float32."""
+    _cuda(q, k, v, state, out, bg, ww, w0, u)
+    T = q.shape[0]
+    for t in (q, k, v):
+        assert t.dtype == torch.float32 and t.dim() == 2 and t.shape[0] == T and t.stride(1) == 1
+        assert T == 1 or t.stride(0) == q.stride(0), "q, k and v rows must be equally far apart"
+    assert q.shape[1] == k.shape[1] == (H // rep) * dk and v.shape[1] == H * dv
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, dv, dk)
+    assert out.shape == (T, H, dv) and out.is_contiguous() and out.dtype == torch.float32
     if mode == SCAN_DELTA:
         assert bg is not None and bg.shape == (T, 2 * H) and bg.is_contiguous() and bg.dtype == torch.float32
     else:
         assert ww.dtype == torch.float32 and ww.shape == (T, H * dk) and ww.stride(1) == 1
         assert w0.numel() == H * dk and u.numel() == H * dk and w0.is_contiguous() and u.is_contiguous()
+    # the kernel addresses k and v from q's first element; the three may be separate allocations
+    k_off, v_off = (k.data_ptr() - q.data_ptr()) // 4, (v.data_ptr() - q.data_ptr()) // 4
+    stride = q.stride(0) if T > 1 else max(q.shape[1], 4) // 4 * 4
     _check(lib().prism_recurrent_scan(
-        int(mode), _ptr(x), x.stride(0), int(q_off), int(k_off), int(v_off), _ptr(bg), _ptr(ww),
+        int(mode), _ptr(q), stride, 0, k_off, v_off, _ptr(bg), _ptr(ww),
         0 if ww is None else ww.stride(0), _ptr(w0), F32 if w0 is None else _dt(w0), _ptr(u), F32 if u is None else _dt(u),
         _ptr(state), _ptr(ctx.seg_start), _ptr(ctx.state_slots), ctx.S, int(getattr(ctx, "max_q_len", None) or T), H, rep, dk, dv,
         _ptr(out), 1 if decay_ready else 0, _stream()),

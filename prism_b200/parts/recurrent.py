@@ -109,7 +109,8 @@ class GatedDeltaMixer(Mixer):
         if not single:
             ops.state_tail(proj, tail.state, ctx)
         o = ctx.alloc((T, H, dv), torch.float32)
-        ops.recurrent_scan(ops.SCAN_DELTA, qkv, 0, G * dk, 2 * G * dk, state.state, ctx, H, H // G, dk, dv, o, bg=bg)
+        ops.recurrent_scan(ops.SCAN_DELTA, qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], state.state, ctx,
+                           H, H // G, dk, dv, o, bg=bg)
         ops.headnorm_gate(o, proj[:, self.g_off:self.g_off + H * dv], self.w["norm"], self.eps, self.out_scale, out)
 
     def forward(self, ctx, x, cache):
@@ -175,16 +176,16 @@ class WKVMixer(Mixer):
         ops.shift_mix(x, prev.state, self.mu, ctx, mixes, keep_prev=ctx.decode_only)
         if not ctx.decode_only:
             ops.state_tail(x, prev.state, ctx)
-        # float32 rows [r | k | v | g | low]: each block of columns from its own mix
-        proj = ops.linear_grouped(mixes, self.w["in_w"], (A, A, A, A, self.rank), torch.float32)
+        # float32 r, k, v, g and the decay's first product, each from its own mix
+        r, k, v, g, low = ops.linear_grouped(mixes, self.w["in_w"], (A, A, A, A, self.rank), torch.float32)
         # tanh, the second product, the offset and both exponentials in one launch: the decay of every key channel
         ww = ctx.alloc((T, A), torch.float32)
-        ops.lowrank_decay(proj[:, 4 * A:], self.w2t, self.w["w0"], ww)
+        ops.lowrank_decay(low, self.w2t, self.w["w0"], ww)
         o = ctx.alloc((T, H, d), torch.float32)
-        ops.recurrent_scan(ops.SCAN_BONUS, proj, 0, A, 2 * A, state.state, ctx, H, 1, d, d, o,
+        ops.recurrent_scan(ops.SCAN_BONUS, r, k, v, state.state, ctx, H, 1, d, d, o,
                            ww=ww, w0=self.w["w0"], u=self.w["u"], decay_ready=True)
         inner = ctx.alloc((T, A), ctx.dtype)
-        ops.headnorm_gate(o, proj[:, 3 * A:4 * A], self.w["norm"], self.eps, self.out_scale, inner)
+        ops.headnorm_gate(o, g, self.w["norm"], self.eps, self.out_scale, inner)
         return ops.linear_delta(inner, self.w["o_w"], None, f32=True)
 
 

@@ -242,7 +242,7 @@ def test_delta_rule_scan_in_pieces_against_the_plain_loop(G, rep, dk, dv):
         bg = torch.cat([data[r][1][a:a + n] for r, (a, n) in act]).to(DEV).contiguous()
         ctx = step_ctx([n for _, (_, n) in act], [(2, 0)[r] for r, _ in act])
         o = torch.empty(x.shape[0], H, dv, device=DEV)
-        ops.recurrent_scan(ops.SCAN_DELTA, x, 0, G * dk, 2 * G * dk, state, ctx, H, rep, dk, dv, o, bg=bg)
+        ops.recurrent_scan(ops.SCAN_DELTA, x[:, :G * dk], x[:, G * dk:2 * G * dk], x[:, 2 * G * dk:], state, ctx, H, rep, dk, dv, o, bg=bg)
         at = 0
         for r, (a, n) in act:
             got[r][a:a + n] = o[at:at + n].cpu()
@@ -281,7 +281,11 @@ def test_bonus_scan_in_pieces_against_the_plain_loop(H, d):
         ww = torch.cat([data[r][1][a:a + n] for r, (a, n) in act]).to(DEV)
         ctx = step_ctx([n for _, (_, n) in act], [(1, 2)[r] for r, _ in act])
         o = torch.empty(x.shape[0], H, d, device=DEV)
-        ops.recurrent_scan(ops.SCAN_BONUS, x, 0, A, 2 * A, state, ctx, H, 1, d, d, o, ww=ww, w0=w0.to(DEV), u=u.to(DEV))
+        if step % 2:      # r, k, v as three products of their own (separate allocations) ...
+            r_, k_, v_ = (x[:, i * A:(i + 1) * A].clone() for i in range(3))
+        else:             # ... or as column blocks of one
+            r_, k_, v_ = (x[:, i * A:(i + 1) * A] for i in range(3))
+        ops.recurrent_scan(ops.SCAN_BONUS, r_, k_, v_, state, ctx, H, 1, d, d, o, ww=ww, w0=w0.to(DEV), u=u.to(DEV))
         at = 0
         for r, (a, n) in act:
             got[r][a:a + n] = o[at:at + n].cpu()
@@ -410,12 +414,12 @@ def test_projections_that_each_read_their_own_input_as_one_product(T, A, R, K):
     g = torch.Generator().manual_seed(T + A)
     xs = torch.randn(5, T, K, generator=g).to(torch.bfloat16)
     w = (torch.randn(4 * A + R, K, generator=g) / K ** 0.5).to(torch.bfloat16)
-    out = ops.linear_grouped(xs.to(DEV), w.to(DEV), (A, A, A, A, R), torch.float32).cpu()
+    out = torch.cat(ops.linear_grouped(xs.to(DEV), w.to(DEV), (A, A, A, A, R), torch.float32), 1).cpu()
     ref = torch.cat([xs[i].float() @ w[i * A:(i * A + R if i == 4 else (i + 1) * A)].float().T for i in range(5)], 1)
     assert out.shape == (T, 4 * A + R)
     assert float((out - ref).abs().max()) <= 2e-3 * max(1.0, float(ref.abs().max()))
     xs32, w32 = xs.float().to(DEV), w.float().to(DEV)
-    out32 = ops.linear_grouped(xs32, w32, (A, A, A, A, R), torch.float32).cpu()
+    out32 = torch.cat(ops.linear_grouped(xs32, w32, (A, A, A, A, R), torch.float32), 1).cpu()
     assert float((out32 - ref).abs().max()) <= 1e-4 * max(1.0, float(ref.abs().max()))
 
 
