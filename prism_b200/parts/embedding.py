@@ -29,7 +29,10 @@ class TokenEmbedding(Embedding):
         out = ctx.alloc((ctx.T, self.hidden_size), ops.torch.float32)
         ops.embed(ctx.token_ids, self.w["weight"], out, ctx.err, self.scale)
         if self.norm is not None:
-            ops.rms_rows(out, self.norm.w["weight"], self.norm.eps, out)
+            # in place on the float32 rows; the same launch leaves their copy in the compute dtype for the first
+            # block's matrix products (a block that norms after the sum looks for it under this key)
+            h = self.norm.forward_post(ctx, out, None, 1.0)
+            ctx.scratch["postnorm_rows"], ctx.scratch["postnorm_rows_of"] = h, out
         return out
 
 
